@@ -1,0 +1,154 @@
+"""Transformer building blocks: RMSNorm, fused-add RMSNorm, RoPE, GQA attention, SwiGLU MLP, Block.
+
+Mirrors the behaviour of the reference layers (nanonemo/model/layers.py:21-161) with two
+structural differences chosen for the Blackwell GEMM path:
+
+* the Q, K and V projections are one parameter ``wqkv`` of shape ``[(H + 2*KVH) * hd, d]`` and the
+  gate and up projections one parameter ``w_gu`` of shape ``[2 * d_ff, d]``, so each is a single
+  wide GEMM (N = 1280 and N = 4096 at the 114M shape) instead of three / two narrow ones;
+* every operator goes through ``nanonemo_b200.ops``; the ``impl`` string picked by the config is
+  either ``torch`` (plain PyTorch, the oracle and the CPU path) or ``sm100`` (hand-written CUDA).
+
+``split_qkv`` / ``split_gu`` give the per-projection views for export to the reference / HF layout.
+"""
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+from torch.nn.attention import SDPBackend, sdpa_kernel
+
+from nanonemo_b200 import ops
+from nanonemo_b200.models.config import ModelConfig
+
+
+class Linear(nn.Module):
+    """Bias-free linear layer. ``impl`` = torch (F.linear / cuBLAS) | sm100 (tcgen05 GEMM) | mxfp8."""
+
+    def __init__(self, in_features: int, out_features: int, impl: str = "torch"):
+        super().__init__()
+        self.in_features, self.out_features, self.impl = in_features, out_features, impl
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, impl=self.impl)
+
+    def extra_repr(self) -> str:
+        return f"in={self.in_features}, out={self.out_features}, impl={self.impl}"
+
+
+def make_linear(cfg: ModelConfig, in_features: int, out_features: int) -> Linear:
+    return Linear(in_features, out_features, cfg.resolved().linear_impl)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rms_norm_torch(x, self.weight, self.eps)
+
+
+class AddRMSNorm(RMSNorm):
+    """forward(x, delta) -> (rmsnorm(x + delta), x + delta); delta=None normalises x alone.
+
+    The residual stream travels as (x, delta) so the pending add and the norm are one pass over
+    memory (reference contract: nanonemo/model/layers.py:34-52).
+    """
+
+    def __init__(self, dim: int, eps: float = 1e-5, impl: str = "torch"):
+        super().__init__(dim, eps)
+        self.impl = impl
+
+    def forward(self, x, delta=None):
+        return ops.add_rms_norm(x, delta, self.weight, self.eps, impl=self.impl)
+
+
+def rope_cache(head_dim: int, max_seq_len: int, base: float = 10000.0, device=None):
+    """cos/sin tables of shape (max_seq_len, head_dim // 2) in fp32; angle[m, i] = m * base^(-2i/hd)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    pos = torch.arange(max_seq_len, device=device, dtype=torch.float32)
+    angles = torch.outer(pos, inv_freq)
+    return angles.cos(), angles.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE on x of shape (B, H, T, hd): pairs dimension i with i + hd/2, fp32 math."""
+    return ops.rope_torch(x, cos, sin, seq_dim=-2)
+
+
+class Attention(nn.Module):
+    """Causal grouped-query attention: n_heads query heads share n_kv_heads K/V heads."""
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        r = cfg.resolved()
+        self.n_heads, self.n_kv_heads, self.head_dim = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        self.q_dim, self.kv_dim = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+        self.backend = {"math": SDPBackend.MATH, "mem_efficient": SDPBackend.EFFICIENT_ATTENTION}[cfg.attn_backend]
+        self.wqkv = make_linear(cfg, cfg.d_model, self.q_dim + 2 * self.kv_dim)
+        self.wo = make_linear(cfg, self.q_dim, cfg.d_model)
+        self.rope_impl, self.attn_impl = r.rope_kernel, r.attn_kernel
+
+    def split_qkv(self):
+        """(wq, wk, wv) views of the fused projection weight."""
+        return self.wqkv.weight.split((self.q_dim, self.kv_dim, self.kv_dim), dim=0)
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        B, T, _ = x.shape
+        H, KVH, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.wqkv(x)  # (B, T, (H + 2 KVH) hd)
+        if self.rope_impl == "sm100" or self.attn_impl == "sm100":
+            # Packed path: RoPE rewrites the Q and K columns of the packed projection in one
+            # launch, attention reads Q/K/V heads from it through strides and each query head
+            # reads its own KV head directly (no repeat_interleave, no transposes).
+            qkv = ops.rope_qkv(qkv, cos, sin, H, KVH, hd, impl=self.rope_impl)
+            y = ops.attention_packed(qkv, H, KVH, hd, impl=self.attn_impl, backend=self.backend)
+            return self.wo(y)
+        q, k, v = qkv.split((self.q_dim, self.kv_dim, self.kv_dim), dim=-1)
+        q = apply_rope(q.view(B, T, H, hd).transpose(1, 2), cos, sin)
+        k = apply_rope(k.view(B, T, KVH, hd).transpose(1, 2), cos, sin)
+        v = v.view(B, T, KVH, hd).transpose(1, 2)
+        y = ops.attention_torch(q, k, v, self.backend)  # (B, H, T, hd)
+        return self.wo(y.transpose(1, 2).reshape(B, T, -1))
+
+
+def silu_mul(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    return F.silu(g) * u
+
+
+class MLP(nn.Module):
+    """SwiGLU feed-forward: down(silu(gate(x)) * up(x)) with gate and up as one GEMM."""
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        r = cfg.resolved()
+        self.d_ff = cfg.d_ff
+        self.w_gu = make_linear(cfg, cfg.d_model, 2 * cfg.d_ff)  # rows [0, d_ff) = gate, [d_ff, 2 d_ff) = up
+        self.w_down = make_linear(cfg, cfg.d_ff, cfg.d_model)
+        self.act_impl = r.swiglu_kernel
+
+    def split_gu(self):
+        return self.w_gu.weight.split((self.d_ff, self.d_ff), dim=0)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.w_down(ops.swiglu_packed(self.w_gu(x), impl=self.act_impl))
+
+
+class Block(nn.Module):
+    """Pre-norm block. Input (x, delta) with delta the previous sublayer output not yet added to x;
+    output (x', delta') in the same convention (reference: nanonemo/model/layers.py:141-161)."""
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        impl = cfg.resolved().norm_kernel
+        self.norm_attn = AddRMSNorm(cfg.d_model, cfg.norm_eps, impl)
+        self.attn = Attention(cfg)
+        self.norm_mlp = AddRMSNorm(cfg.d_model, cfg.norm_eps, impl)
+        self.mlp = MLP(cfg)
+
+    def forward(self, x, cos, sin, delta=None):
+        h, x = self.norm_attn(x, delta)
+        h, x = self.norm_mlp(x, self.attn(h, cos, sin))
+        return x, self.mlp(h)

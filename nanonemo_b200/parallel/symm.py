@@ -1,0 +1,94 @@
+"""Symmetric-memory layer: buffers mapped into every peer GPU, and the collectives written on them.
+
+``torch.distributed._symmetric_memory`` is used only as the allocator and handshake (it exchanges
+the cuMem handles and gives each rank the peers' device pointers, and the NVLS multicast address
+when the driver exposes one). The data movement is this framework's own kernels (csrc/comm.cu):
+peer loads and stores issued from inside the kernel, synchronised by epoch-numbered flags in a
+second symmetric buffer with system-scope release/acquire, every wait bounded (on expiry the kernel
+records {code, rank, peer, block} in a status word and returns; ``check_status`` raises on the host).
+
+The reference has no counterpart: its collectives are NCCL calls made by torch DDP / FSDP2 / DTensor
+(nanonemo/distributed/*.py).
+"""
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+FLAG_WORDS = 1 << 16  # uint32 flags per rank (phase x block x peer slots)
+STATUS_WORDS = 8
+
+
+def fused_available(d, comm: str) -> bool:
+    if comm == "nccl" or not str(d.device).startswith("cuda"):
+        return False
+    from nanonemo_b200.ops import _lib
+
+    ok = _lib.available()
+    if comm == "fused" and not ok:
+        raise RuntimeError("comm=fused needs a CUDA device and the built kernel library")
+    return ok
+
+
+class SymmetricBuffer:
+    """A tensor allocated in symmetric memory plus the peers' pointers to it."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group or dist.group.WORLD
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group=group)
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.ptr_array = (ctypes.c_void_p * 16)(*self.peer_ptrs)
+
+
+class SymmetricAllReduce:
+    """In-place two-shot all-reduce (+ scale) over ranges of one symmetric fp32 buffer."""
+
+    def __init__(self, data: SymmetricBuffer, group=None):
+        self.data = data
+        dev = data.tensor.device
+        self.flags = SymmetricBuffer(FLAG_WORDS, torch.int32, dev, group)
+        self.flags.tensor.zero_()
+        self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=dev)
+        self.epoch = 0
+        self.blocks = int(os.environ.get("NANONEMO_COMM_BLOCKS", "32"))
+        self.use_multimem = bool(data.multicast_ptr) and os.environ.get("NANONEMO_MULTIMEM", "0") == "1"
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)
+
+    def all_reduce_(self, lo: int, hi: int, scale: float):
+        from nanonemo_b200.ops import _lib
+
+        self.epoch += 1
+        _lib.call("nnb_allreduce_f32", self.data.ptr_array, self.flags.ptr_array,
+                  ctypes.c_void_p(self.data.multicast_ptr if self.use_multimem else 0),
+                  _lib.ptr(self.status), _lib.i32(self.data.rank), _lib.i32(self.data.world),
+                  _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale), _lib.i32(self.epoch), _lib.i32(self.blocks),
+                  ctypes.c_void_p(_lib.stream_ptr()))
+
+    def check_status(self):
+        st = self.status.tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"fused collective gave up waiting: code={st[0]} rank={st[1]} peer={st[2]} "
+                               f"block={st[3]} epoch={st[4]}")
+
+
+def make_grad_allreduce(d, comm: str, group=None):
+    """Returns (grad_alloc, finish): `grad_alloc(numel)` allocates the flat gradient buffer (in
+    symmetric memory when the fused path is on), `finish(store)` returns the SymmetricAllReduce
+    bound to it, or None when gradients are reduced with torch.distributed."""
+    if not fused_available(d, comm):
+        return None, lambda store: None
+    box = {}
+
+    def grad_alloc(numel: int):
+        box["buf"] = SymmetricBuffer(numel, torch.float32, d.device, group)
+        return box["buf"].tensor
+
+    return grad_alloc, lambda store: SymmetricAllReduce(box["buf"], group)
