@@ -120,7 +120,7 @@ def attention_packed(qkv, n_heads, n_kv_heads, head_dim, impl="torch", backend=S
         v = v.view(B, T, n_kv_heads, head_dim).transpose(1, 2)
         return attention_torch(q, k, v, backend).transpose(1, 2).reshape(B, T, qd)
     _need_cuda(qkv, "attention_packed")
-    from nanonemo_b200.ops.flash_attn import flash_attn_packed
+    from nanonemo_b200.ops.attention import flash_attn_packed
 
     return flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)
 
@@ -130,7 +130,7 @@ def flash_attn(q, k, v, impl="sm100"):
     if impl == "torch":
         return attention_torch(q, k, v)
     _need_cuda(q, "flash_attn")
-    from nanonemo_b200.ops.flash_attn import flash_attn as f
+    from nanonemo_b200.ops.attention import flash_attn as f
 
     return f(q, k, v)
 
@@ -139,7 +139,7 @@ def swiglu(g, u, impl="torch"):
     if impl == "torch":
         return swiglu_torch(g, u)
     _need_cuda(g, "swiglu")
-    from nanonemo_b200.ops.swiglu import swiglu as f
+    from nanonemo_b200.ops.swiglu_act import swiglu as f
 
     return f(g, u)
 
@@ -150,7 +150,7 @@ def swiglu_packed(gu, impl="torch"):
         g, u = gu.chunk(2, dim=-1)
         return swiglu_torch(g, u)
     _need_cuda(gu, "swiglu_packed")
-    from nanonemo_b200.ops.swiglu import swiglu_packed as f
+    from nanonemo_b200.ops.swiglu_act import swiglu_packed as f
 
     return f(gu)
 
@@ -159,7 +159,7 @@ def embedding(idx, weight, impl="torch"):
     if impl == "torch":
         return F.embedding(idx, weight)
     _need_cuda(weight, "embedding")
-    from nanonemo_b200.ops.embedding import embedding as f
+    from nanonemo_b200.ops.embed import embedding as f
 
     return f(idx, weight)
 
