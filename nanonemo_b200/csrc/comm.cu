@@ -1,0 +1,227 @@
+// Collectives over NVLink 5 / NVSwitch written as kernels on symmetric memory: every rank holds the
+// same buffer at the same offsets and the kernel is given all peers' device pointers, so it reduces,
+// scatters and gathers with plain peer loads and stores (ld/st.global on a peer address) — or, when a
+// multicast address is supplied, with multimem.ld_reduce / multimem.st so the switch does the sum and
+// the broadcast. No NCCL call is involved.
+//
+//   nnb_allreduce_f32       in-place two-shot all-reduce of a range, fused with a scale (the 1/world
+//                           gradient average): rank r reduces slice r from all peers and writes the
+//                           result into every peer's buffer.
+//   nnb_reduce_scatter_f32  rank r's slice of the sum (+ scale) into a local shard buffer, and the sum
+//                           of squares of that shard for global-norm clipping.
+//   nnb_allgather_bytes     every rank's shard into the local full buffer (pull).
+//
+// Synchronisation: a second symmetric buffer of uint32 flags, one slot per (phase, block, source
+// rank), written with st.release.sys and polled locally with ld.acquire.sys; values are the call's
+// epoch number, so flags never need resetting (and CUDA-graph replays would need none either).
+// Block b of a rank only ever talks to block b of its peers, so the kernel needs no grid-wide sync.
+// EVERY wait is bounded: after kPollLimit polls the block records {code, rank, peer, block, epoch} in
+// the status words and carries on to the end, and the host raises after the next synchronisation.
+// Nothing here waits on a kernel of the same GPU: one rank = one process = one GPU.
+//
+// The reference reaches NCCL through torch DDP / FSDP2 / DTensor (nanonemo/distributed/*.py).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxWorld = 16;
+constexpr uint32_t kPollLimit = 1u << 22;
+constexpr int kCommThreads = 512;
+
+struct Peers {
+  void* data[kMaxWorld];
+  uint32_t* flags[kMaxWorld];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.relaxed.sys.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// Cross-rank barrier among the blocks with this block's index: signal every peer, then wait for
+// every peer. Returns false if a wait ran out (status recorded).
+__device__ bool block_barrier(const Peers& P, int rank, int world, int phase, uint32_t epoch, int* status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __threadfence_system();
+  __syncthreads();
+  const int slot = (phase * gridDim.x + blockIdx.x) * kMaxWorld;
+  if ((int)threadIdx.x < world) {
+    const int peer = threadIdx.x;
+    st_release_sys(P.flags[peer] + slot + rank, epoch);
+    const uint32_t* mine = P.flags[rank] + slot + peer;
+    uint32_t polls = 0;
+    // epochs only grow; signed distance tolerates wrap-around
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (++polls > kPollLimit) {
+        s_fail = 1;
+        if (status != nullptr && atomicCAS(status, 0, 10 + phase) == 0) {
+          status[1] = rank; status[2] = peer; status[3] = blockIdx.x; status[4] = (int)epoch;
+        }
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+__global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, float* mc, int rank, int world, long long lo,
+                                                                     long long n, float scale, uint32_t epoch, int* status) {
+  const bool ok = block_barrier(P, rank, world, 0, epoch, status);  // every peer's inputs are final
+  const long long per = ((n + world - 1) / world + 3) & ~3LL;       // slice length, multiple of 4
+  const long long s0 = min((long long)rank * per, n), s1 = min(s0 + per, n);
+  const long long n4 = (s1 - s0) >> 2;
+  if (ok) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+      const long long off = lo + s0 + 4 * i;
+      float4 acc;
+      if (mc != nullptr) {
+        acc = multimem_ld_reduce_f4(mc + off);
+      } else {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {  // fixed order: the result does not depend on who reduces
+          const float4 v = ld_peer_f4(static_cast<const float*>(P.data[r]) + off);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      if (mc != nullptr) {
+        multimem_st_f4(mc + off, acc);
+      } else {
+        for (int r = 0; r < world; ++r) *reinterpret_cast<float4*>(static_cast<float*>(P.data[r]) + off) = acc;
+      }
+    }
+  }
+  block_barrier(P, rank, world, 1, epoch, status);  // every peer's results have landed here
+}
+
+// out[i] = scale * sum_r data[r][lo + rank*per + i]; sumsq_out += sum(out^2) (one atomic per block).
+__global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers P, float* out, float* sumsq_out, int rank, int world,
+                                                                          long long lo, long long per, float scale,
+                                                                          uint32_t epoch, int* status) {
+  __shared__ float s_part[kCommThreads / 32];
+  const bool ok = block_barrier(P, rank, world, 0, epoch, status);
+  const long long n4 = per >> 2;
+  float ss = 0.f;
+  if (ok) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+      const long long off = lo + (long long)rank * per + 4 * i;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float4 v = ld_peer_f4(static_cast<const float*>(P.data[r]) + off);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      reinterpret_cast<float4*>(out)[i] = acc;
+      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+  }
+  if (sumsq_out != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v = threadIdx.x < kCommThreads / 32 ? s_part[threadIdx.x] : 0.f;
+      v = warp_sum(v);
+      if (threadIdx.x == 0) atomicAdd(sumsq_out, v);
+    }
+  }
+  // peers may overwrite their inputs only after everybody has read them
+  block_barrier(P, rank, world, 1, epoch, status);
+}
+
+// local_full[r*per_bytes .. ] = peer r's shard (its bytes [src_off, src_off + per_bytes) ), 16-byte units.
+__global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_t* local_full, int rank, int world,
+                                                                 long long src_off, long long per_bytes, uint32_t epoch,
+                                                                 int* status) {
+  const bool ok = block_barrier(P, rank, world, 0, epoch, status);  // every peer's shard is final
+  const long long n16 = per_bytes >> 4;
+  if (ok) {
+    for (int rr = 0; rr < world; ++rr) {
+      const int r = (rank + rr) % world;  // start with the local shard, then spread the peers
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.data[r]) + src_off);
+      uint4* dst = reinterpret_cast<uint4*>(local_full + (long long)r * per_bytes);
+      for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+        uint4 v;
+        asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+        dst[i] = v;
+      }
+    }
+  }
+  block_barrier(P, rank, world, 1, epoch, status);  // shards may be rewritten once everybody has copied them
+}
+
+int fill_peers(Peers& P, void* const* data_ptrs, void* const* flag_ptrs, int world) {
+  if (world < 1 || world > kMaxWorld) {
+    nnb_set_error("comm: world size %d not supported (1..%d)", world, kMaxWorld);
+    return -1;
+  }
+  for (int r = 0; r < kMaxWorld; ++r) {
+    P.data[r] = r < world ? data_ptrs[r] : nullptr;
+    P.flags[r] = r < world ? static_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
+  }
+  return 0;
+}
+
+}  // namespace
+
+// Flag buffer requirement: uint32 [2 phases][blocks][16] per rank, zero before the first call.
+extern "C" int nnb_comm_flag_words(int blocks) { return 2 * blocks * kMaxWorld; }
+
+extern "C" int nnb_allreduce_f32(void* const* data_ptrs, void* const* flag_ptrs, void* multicast_ptr, void* status, int rank,
+                                 int world, long long lo, long long n, float scale, int epoch, int blocks, cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  NNB_REQUIRE(lo % 4 == 0 && n % 4 == 0, "allreduce: range must be 16-byte aligned (lo=%lld n=%lld)", lo, n);
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024, "allreduce: bad block count %d", blocks);
+  if (n == 0) return 0;
+  allreduce_f32_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<float*>(multicast_ptr), rank, world, lo, n, scale,
+                                                        (uint32_t)epoch, static_cast<int*>(status));
+  NNB_LAUNCH_OK("allreduce_f32");
+  return 0;
+}
+
+extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_ptrs, void* out, void* sumsq_out, void* status,
+                                      int rank, int world, long long lo, long long per, float scale, int epoch, int blocks,
+                                      cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  NNB_REQUIRE(lo % 4 == 0 && per % 4 == 0, "reduce_scatter: range must be 16-byte aligned");
+  if (per == 0) return 0;
+  reduce_scatter_f32_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<float*>(out), static_cast<float*>(sumsq_out), rank, world,
+                                                             lo, per, scale, (uint32_t)epoch, static_cast<int*>(status));
+  NNB_LAUNCH_OK("reduce_scatter_f32");
+  return 0;
+}
+
+extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptrs, void* local_full, void* status, int rank,
+                                   int world, long long src_off, long long per_bytes, int epoch, int blocks, cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  NNB_REQUIRE(src_off % 16 == 0 && per_bytes % 16 == 0 && nnb_aligned16(local_full), "allgather: 16-byte alignment required");
+  if (per_bytes == 0) return 0;
+  allgather_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<uint8_t*>(local_full), rank, world, src_off, per_bytes,
+                                                    (uint32_t)epoch, static_cast<int*>(status));
+  NNB_LAUNCH_OK("allgather");
+  return 0;
+}

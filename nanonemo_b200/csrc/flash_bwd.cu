@@ -1,0 +1,369 @@
+// Causal grouped-query FlashAttention backward on tcgen05 / TMEM / TMA for sm_100a (head_dim 64).
+//
+// One CTA owns 128 keys of one (batch, KV head) and visits every (query head of the group, query tile)
+// at or after its keys; dK and dV of the tile accumulate in TMEM over the whole GQA group, so they are
+// written once and need no atomics (as in the reference kernel, nanonemo/kernels/cuda/flash_attn.cu:
+// 176-340, which keeps them in registers). Per visit, five tensor-core products:
+//     S  = Q K^T            dP = dO V^T                       (M = queries, N = keys, K = head_dim)
+//     P  = exp(S*scale - L) ; dS = P * (dP - D) * scale       (128 compute threads, one per query row)
+//     dV += P^T dO          dK += dS^T Q                      (M = keys, N = head_dim, K = queries)
+//     dQ  = dS K                                              (M = queries, N = head_dim, K = keys)
+// P and dS are written once to shared memory as bf16 [query][key] tiles with the 128-byte swizzle; the
+// same bytes serve as the K-major A operand of dQ and, read through an MN-major descriptor, as the
+// transposed A operand of dV / dK. Q and dO tiles arrive by TMA and are read both K-major (S, dP) and
+// MN-major (dK, dV) without any transposed copy. dQ partial tiles leave through a swizzled fp32
+// staging tile and a TMA reduce-add (cp.reduce.async.bulk.tensor .add.f32) into an fp32 buffer that a
+// small kernel converts at the end. D = rowsum(dO * O) is a pre-pass kernel in this file.
+// 192 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 compute. All waits are bounded.
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BQ = 128, BKV = 128, HD = 64;
+constexpr int kThreads = 192;
+constexpr int kTile16 = 128 * 64 * 2;     // a [128 x 64] 16-bit tile = 16 KB
+constexpr int kStagesQ = 2;
+// shared memory map (bytes)
+constexpr int kOffK = 0, kOffV = kTile16, kOffQdO = 2 * kTile16;               // ring of (Q | dO)
+constexpr int kOffP = kOffQdO + kStagesQ * 2 * kTile16, kOffdS = kOffP + 2 * kTile16;
+constexpr int kOffStage = kOffdS + 2 * kTile16;                                // fp32 [128 x 64] = 32 KB
+constexpr int kOffBars = kOffStage + 2 * kTile16;
+constexpr int kSmem = kOffBars + 256 + 1024;
+// tensor memory columns
+constexpr int kColS = 0, kColdP = 128, kColdV = 256, kColdK = 320, kColdQ = 384, kTmemCols = 512;
+
+struct BParams {
+  int B, H, KVH, T, n_q_tiles, group;
+  float scale, scale_log2;
+  const float* lse;    // [B, H, T]
+  const float* delta;  // [B, H, T]
+  uint32_t idesc_s, idesc_dkv, idesc_dq;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmdQacc, const __grid_constant__ CUtensorMap tmdK,
+                 const __grid_constant__ CUtensorMap tmdV, const BParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  // barriers: kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full, dq_read
+  const uint32_t bar_kv = smem_u32(bars), bar_qf = bar_kv + 8, bar_qe = bar_qf + 16;
+  const uint32_t bar_sdp = bar_qe + 16, bar_pds = bar_sdp + 8, bar_dq = bar_pds + 8, bar_dqr = bar_dq + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;          // key tile
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int first_qt = (kt * BKV) / BQ;                     // first query tile that can see these keys
+  const int n_qt = p.n_q_tiles - first_qt;                  // query tiles per head of the group
+  const int iters = n_qt * p.group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_kv, 1);
+    for (int s = 0; s < kStagesQ; ++s) {
+      mbar_init(bar_qf + 8 * s, 1);
+      mbar_init(bar_qe + 8 * s, 1);
+    }
+    mbar_init(bar_sdp, 1);
+    mbar_init(bar_pds, 128);
+    mbar_init(bar_dq, 1);
+    mbar_init(bar_dqr, 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  int fail_role = 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(bar_kv, 2 * kTile16);
+      tma_load_4d(s_base + kOffK, &tmK, bar_kv, 0, kvh, kt * BKV, b);
+      tma_load_4d(s_base + kOffV, &tmV, bar_kv, 0, kvh, kt * BKV, b);
+      for (int n = 0; n < iters; ++n) {
+        const int hq = kvh * p.group + n / n_qt, qt = first_qt + n % n_qt;
+        const uint32_t s = n % kStagesQ, ph = (n / kStagesQ) & 1;
+        if (!mbar_wait(bar_qe + 8 * s, ph ^ 1, abort_flag)) { fail_role = 1; break; }
+        const uint32_t dst = s_base + kOffQdO + s * 2 * kTile16;
+        mbar_expect_tx(bar_qf + 8 * s, 2 * kTile16);
+        tma_load_4d(dst, &tmQ, bar_qf + 8 * s, 0, hq, qt * BQ, b);
+        tma_load_4d(dst + kTile16, &tmdO, bar_qf + 8 * s, 0, hq, qt * BQ, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_kv, 0, abort_flag);
+      if (!ok) fail_role = 2;
+      const uint32_t sK = s_base + kOffK, sV = s_base + kOffV, sP = s_base + kOffP, sdS = s_base + kOffdS;
+      for (int n = 0; n < iters && ok; ++n) {
+        const uint32_t s = n % kStagesQ, ph = (n / kStagesQ) & 1;
+        const uint32_t sQ = s_base + kOffQdO + s * 2 * kTile16, sdO = sQ + kTile16;
+        if (!mbar_wait(bar_qf + 8 * s, ph, abort_flag)) { ok = false; fail_role = 2; break; }
+        tc_fence_after();
+        // S = Q K^T and dP = dO V^T: all operands K-major, 4 k-steps of 16 over head_dim
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem_base + kColS, make_smem_desc(sQ + k * 32, 16, 1024), make_smem_desc(sK + k * 32, 16, 1024), p.idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem_base + kColdP, make_smem_desc(sdO + k * 32, 16, 1024), make_smem_desc(sV + k * 32, 16, 1024), p.idesc_s, k > 0);
+        umma_commit(bar_sdp);
+        if (!mbar_wait(bar_pds, n & 1, abort_flag)) { ok = false; fail_role = 2; break; }
+        if (n > 0 && !mbar_wait(bar_dqr, (n - 1) & 1, abort_flag)) { ok = false; fail_role = 2; break; }
+        tc_fence_after();
+        // dV += P^T dO and dK += dS^T Q: A = [query][key] tile read MN-major (M = keys: two 64-key groups
+        // 16 KB apart), B = [query][hd] tile read MN-major; 8 k-steps of 16 query rows (2048 bytes each).
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          umma_f16(tmem_base + kColdV, make_smem_desc(sP + k * 2048, kTile16, 1024), make_smem_desc(sdO + k * 2048, kTile16, 1024),
+                   p.idesc_dkv, (n > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          umma_f16(tmem_base + kColdK, make_smem_desc(sdS + k * 2048, kTile16, 1024), make_smem_desc(sQ + k * 2048, kTile16, 1024),
+                   p.idesc_dkv, (n > 0 || k > 0) ? 1u : 0u);
+        // dQ = dS K: A = dS K-major over keys (two 64-key blocks), B = K tile read MN-major (16 key rows per step)
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          umma_f16(tmem_base + kColdQ, make_smem_desc(sdS + (k / 4) * kTile16 + (k % 4) * 32, 16, 1024),
+                   make_smem_desc(sK + k * 2048, kTile16, 1024), p.idesc_dq, k > 0);
+        umma_commit(bar_dq);
+        umma_commit(bar_qe + 8 * s);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps (one thread per query row)
+    const int q = warp & 3, row = q * 32 + lane, sw = row & 7;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* my_p = smem + kOffP + row * 128;
+    uint8_t* my_ds = smem + kOffdS + row * 128;
+    uint8_t* my_stage = smem + kOffStage + row * 128;
+    const int key0 = kt * BKV;
+    bool ok = true;
+    constexpr float kLog2e = 1.4426950408889634f;
+    for (int n = 0; n < iters; ++n) {
+      const int hq = kvh * p.group + n / n_qt, qt = first_qt + n % n_qt;
+      const int qi = qt * BQ + row;
+      const bool row_ok = qi < p.T;
+      const size_t stat = ((size_t)b * p.H + hq) * p.T + (row_ok ? qi : 0);
+      const float L = row_ok ? p.lse[stat] * kLog2e : 0.f;
+      const float D = row_ok ? p.delta[stat] : 0.f;
+      if (!mbar_wait(bar_sdp, n & 1, abort_flag)) { ok = false; fail_role = 3; break; }
+      tc_fence_after();
+      const bool need_mask = key0 + BKV - 1 > qt * BQ;
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(t_lane + kColS + c * 32, rs);
+        tmem_ld_32x32b_x32(t_lane + kColdP + c * 32, rp);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + c * 32 + i + e;
+            const bool keep = row_ok && key < p.T && (!need_mask || key <= qi);
+            const float prob = keep ? exp2f(__uint_as_float(rs[i + e]) * p.scale_log2 - L) : 0.f;
+            pv[e] = prob;
+            dv[e] = prob * (__uint_as_float(rp[i + e]) - D) * p.scale;
+          }
+          __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]), d2 = __floats2bfloat162_rn(dv[0], dv[1]);
+          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
+          dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
+        }
+        const int blk = (c >> 1) * kTile16;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int chunk = (((c & 1) * 4 + jj) ^ sw) << 4;
+          *reinterpret_cast<uint4*>(my_p + blk + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+          *reinterpret_cast<uint4*>(my_ds + blk + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar_pds);
+      // dQ partial tile: TMEM -> swizzled fp32 staging (two [128 x 32] boxes) -> TMA reduce-add
+      if (!mbar_wait(bar_dq, n & 1, abort_flag)) { ok = false; fail_role = 3; break; }
+      tc_fence_after();
+      if (row == 0) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
+      named_barrier_sync(1, 128);
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_lane + kColdQ + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj)
+          *reinterpret_cast<uint4*>(my_stage + c * kTile16 + ((jj ^ sw) << 4)) = make_uint4(r[4 * jj], r[4 * jj + 1], r[4 * jj + 2], r[4 * jj + 3]);
+      }
+      tc_fence_before();
+      mbar_arrive(bar_dqr);
+      fence_proxy_async_smem();
+      named_barrier_sync(1, 128);
+      if (row == 0) {
+        tma_reduce_add_4d(&tmdQacc, s_base + kOffStage, 0, hq, qt * BQ, b);
+        tma_reduce_add_4d(&tmdQacc, s_base + kOffStage + kTile16, 32, hq, qt * BQ, b);
+        tma_commit_group();
+      }
+    }
+    // dK, dV of this key tile: TMEM -> bf16 staging (reuse the P / dS tiles) -> TMA store
+    if (ok && iters > 0) {
+      // bar_dq of the last visit was awaited above, so every MMA (including dV / dK accumulation) has completed
+      if (row == 0) tma_wait_group_read<0>();
+      named_barrier_sync(1, 128);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint8_t* dst = (which == 0 ? smem + kOffP : smem + kOffdS) + row * 128;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(t_lane + (which == 0 ? kColdV : kColdK), r0);
+        tmem_ld_32x32b_x32(t_lane + (which == 0 ? kColdV : kColdK) + 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = (jj & 3) * 8 + 2 * e;
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
+            w[e] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          *reinterpret_cast<uint4*>(dst + ((jj ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      named_barrier_sync(1, 128);
+      if (row == 0) {
+        tma_store_4d(&tmdV, s_base + kOffP, 0, kvh, kt * BKV, b);
+        tma_store_4d(&tmdK, s_base + kOffdS, 0, kvh, kt * BKV, b);
+        tma_commit_group();
+      }
+    }
+    if (row == 0) tma_wait_group<0>();
+  }
+
+  if (fail_role != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, 3) == 0) {
+      p.status[1] = fail_role;
+      p.status[2] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+      p.status[3] = 0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (b, t, h) row of 64 elements.
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                   float* __restrict__ delta, int B, int T, int H, long long o_sb, long long o_st,
+                                   long long o_sh, long long do_sb, long long do_st, long long do_sh) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)B * T * H;
+  if (w >= rows) return;
+  const int h = (int)(w % H);
+  const long long bt = w / H;
+  const int t = (int)(bt % T), b = (int)(bt / T);
+  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + b * o_sb + t * o_st + h * o_sh)[lane];
+  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + b * do_sb + t * do_st + h * do_sh)[lane];
+  const float2 af = __bfloat1622float2(a), gf = __bfloat1622float2(g);
+  const float s = warp_sum(af.x * gf.x + af.y * gf.y);
+  if (lane == 0) delta[((size_t)b * H + h) * T + t] = s;
+}
+
+// dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous)
+__global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int H,
+                                        int T, long long sb, long long st, long long sh) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;  // one thread per 8 elements
+  const long long total = rows * (HD / 8);
+  if (idx >= total) return;
+  const long long r = idx / (HD / 8);
+  const int j = (int)(idx % (HD / 8)) * 8;
+  const int h = (int)(r % H);
+  const long long bt = r / H;
+  const int t = (int)(bt % T);
+  const long long b = bt / T;
+  float v[8];
+  Chunk8<float>::load(acc + r * HD + j, v);
+  Chunk8<__nv_bfloat16>::store(dq + b * sb + t * st + h * sh + j, v);
+}
+
+}  // namespace
+
+// All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16.
+// lse: fp32 [B, H, T] from the forward pass; delta: fp32 [B, H, T] scratch (written here);
+// dq_acc: fp32 [B, T, H, 64] contiguous, ZERO on entry (partial tiles are reduce-added into it).
+extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
+                             void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, int hd,
+                             long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st, long long k_sh,
+                             long long v_sb, long long v_st, long long v_sh, long long o_sb, long long o_st, long long o_sh,
+                             long long do_sb, long long do_st, long long do_sh, long long dq_sb, long long dq_st,
+                             long long dq_sh, long long dk_sb, long long dk_st, long long dk_sh, long long dv_sb,
+                             long long dv_st, long long dv_sh, float scale, int dtype, void* status, cudaStream_t st) {
+  NNB_REQUIRE(hd == HD, "flash_bwd: head_dim %d not supported (64)", hd);
+  NNB_REQUIRE(dtype == NNB_BF16, "flash_bwd: bf16 only");
+  NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_bwd: bad shape");
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+  if (!nnb_make_tmap_4d(&tq, dt, 2, q, hd, H, T, B, q_sh * 2, q_st * 2, q_sb * 2, 64, 1, BQ, "flash_bwd Q")) return -4;
+  if (!nnb_make_tmap_4d(&tk, dt, 2, k, hd, KVH, T, B, k_sh * 2, k_st * 2, k_sb * 2, 64, 1, BKV, "flash_bwd K")) return -4;
+  if (!nnb_make_tmap_4d(&tv, dt, 2, v, hd, KVH, T, B, v_sh * 2, v_st * 2, v_sb * 2, 64, 1, BKV, "flash_bwd V")) return -4;
+  if (!nnb_make_tmap_4d(&tdo, dt, 2, d_o, hd, H, T, B, do_sh * 2, do_st * 2, do_sb * 2, 64, 1, BQ, "flash_bwd dO")) return -4;
+  if (!nnb_make_tmap_4d(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, hd, H, T, B, (uint64_t)hd * 4, (uint64_t)H * hd * 4,
+                        (uint64_t)T * H * hd * 4, 32, 1, BQ, "flash_bwd dQ acc")) return -4;
+  if (!nnb_make_tmap_4d(&tdk, dt, 2, dk, hd, KVH, T, B, dk_sh * 2, dk_st * 2, dk_sb * 2, 64, 1, BKV, "flash_bwd dK")) return -4;
+  if (!nnb_make_tmap_4d(&tdv, dt, 2, dv, hd, KVH, T, B, dv_sh * 2, dv_st * 2, dv_sb * 2, 64, 1, BKV, "flash_bwd dV")) return -4;
+
+  const long long rows = (long long)B * T * H;
+  flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+                                                                          (float*)delta, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
+  NNB_LAUNCH_OK("flash_delta");
+
+  BParams p{};
+  p.B = B; p.H = H; p.KVH = KVH; p.T = T;
+  p.n_q_tiles = (T + BQ - 1) / BQ;
+  p.group = H / KVH;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = static_cast<const float*>(lse);
+  p.delta = static_cast<const float*>(delta);
+  p.idesc_s = sm100::make_idesc_f16(1, 0, 0, BQ, BKV);
+  p.idesc_dkv = sm100::make_idesc_f16(1, 1, 1, BKV, HD);
+  p.idesc_dq = sm100::make_idesc_f16(1, 0, 1, BQ, HD);
+  p.status = static_cast<int*>(status);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+      nnb_set_error("flash_bwd: cannot reserve %d bytes of shared memory", kSmem);
+      return -3;
+    }
+    configured = true;
+  }
+  dim3 grid((T + BKV - 1) / BKV, KVH, B);
+  flash_bwd_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
+  NNB_LAUNCH_OK("flash_bwd");
+  flash_dq_convert_kernel<<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows,
+                                                                                    H, T, dq_sb, dq_st, dq_sh);
+  NNB_LAUNCH_OK("flash_dq_convert");
+  return 0;
+}

@@ -76,6 +76,34 @@ static inline bool nnb_make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, in
   return true;
 }
 
+// 4-D variant for attention operands: dims (d0 = head_dim [contiguous], d1 = heads, d2 = t, d3 = batch)
+// with byte strides for d1..d3; box = (box0, 1, box2, 1); 128-byte swizzle when box0 * elem_bytes == 128.
+static inline bool nnb_make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                                    uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1_bytes,
+                                    uint64_t s2_bytes, uint64_t s3_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                                    const char* what) {
+  NnbEncodeTiled enc = nnb_encode_fn();
+  if (!enc) { nnb_set_error("%s: cuTensorMapEncodeTiled is not available", what); return false; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1_bytes & 15) || (s2_bytes & 15) || (s3_bytes & 15)) {
+    nnb_set_error("%s: TMA needs a 16-byte aligned base and strides (base=%p strides=%llu,%llu,%llu)", what, base,
+                  (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, (unsigned long long)s3_bytes);
+    return false;
+  }
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1_bytes, s2_bytes, s3_bytes};
+  cuuint32_t box[4] = {box0, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapSwizzle sw = (box0 * elem_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    nnb_set_error("%s: cuTensorMapEncodeTiled(4d) failed with %d (dims %llu,%llu,%llu,%llu)", what, (int)r,
+                  (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, (unsigned long long)d3);
+    return false;
+  }
+  return true;
+}
+
 #ifdef __CUDACC__
 namespace sm100 {
 
@@ -130,6 +158,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -113,3 +113,18 @@ class TokenLoader:
             if state[key] != getattr(self, key):
                 raise ValueError(f"cannot resume: {key} was {state[key]}, now {getattr(self, key)}")
         self.micro_step = state["micro_step"]
+
+
+class DeviceBatches:
+    """`n` batches of a loader staged on the device once and then served round-robin: a data source
+    with no host->device traffic, for device-only timing of the training step."""
+
+    def __init__(self, loader: TokenLoader, n: int):
+        self.batches = [tuple(t.clone() for t in loader.next_batch()) for _ in range(n)]
+        self.micro_step = 0
+        self.loader = loader
+
+    def next_batch(self):
+        b = self.batches[self.micro_step % len(self.batches)]
+        self.micro_step += 1
+        return b

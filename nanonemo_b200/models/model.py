@@ -32,6 +32,20 @@ class NanoNemo(nn.Module):
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
         self.reset_parameters()
+        self._mark_gradient_paths()
+
+    def _mark_gradient_paths(self):
+        """Tell the gradient-ready bookkeeping (parallel/ddp.py) which parameters get their gradient
+        written straight into the flat buffer by an sm100 backward (`_manual_ready`), and that the
+        tied embedding/head weight is complete only after the embedding backward (`_tied_embedding`)."""
+        w = self.tok_emb.weight
+        w._tied_embedding = True
+        w._manual_ready = self.embed_impl == "sm100"
+        for m in self.modules():
+            if isinstance(m, Linear) and m.impl != "torch" and m.weight is not w:
+                m.weight._manual_ready = True
+            if isinstance(m, AddRMSNorm) and m.impl == "sm100":
+                m.weight._manual_ready = True
 
     def reset_parameters(self):
         """N(0, init_std) for every matmul weight and the embedding; the two projections that write

@@ -45,8 +45,9 @@ class _Embedding(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         flat, weight = ctx.saved_tensors
-        if getattr(weight, "_flat_store", None) is not None and weight.grad is not None and weight.grad.dtype == torch.float32:
-            bwd_raw(flat, dout, weight.grad)
+        main = getattr(weight, "_main_grad", None)
+        if main is not None and main.dtype == torch.float32:
+            bwd_raw(flat, dout, main)
             cb = getattr(weight, "_grad_ready_cb", None)
             if cb is not None:
                 cb(weight, True)

@@ -117,12 +117,12 @@ class _Linear(torch.autograd.Function):
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
-            main = weight.grad if getattr(weight, "_flat_store", None) is not None else None
+            main = getattr(weight, "_main_grad", None)
             if main is not None and main.dtype == torch.float32:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
                 cb = getattr(weight, "_grad_ready_cb", None)
-                if cb is not None:
-                    cb(weight, True)
+                if cb is not None and not getattr(weight, "_tied_embedding", False):
+                    cb(weight, True)  # a tied head weight is complete only after the embedding backward
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(weight.dtype)
         return dx, dw

@@ -1,0 +1,77 @@
+"""Fused linear + cross-entropy over the tied LM head: mean CE of ``x @ W^T`` without the logits.
+
+Row chunks of the flattened hidden states go through: logits chunk (tcgen05 GEMM, bf16) -> one-pass
+in-place CE kernel (loss per row, logits overwritten with ``(softmax - onehot) / N``) -> ``dx`` chunk
+and ``dW +=`` (tcgen05 GEMMs, the latter accumulating in fp32). As in the reference operator
+(nanonemo/kernels/triton/linear_ce.py:44-80) the gradients are produced during the forward pass and
+backward only rescales them by the upstream gradient; the chunk is sized for B200 (8192 rows: the
+chunk's logits are 0.8 GB instead of the reference's 512-row chunks).
+"""
+
+import torch
+
+from nanonemo_b200.ops import _lib
+from nanonemo_b200.ops.gemm import _CODE, compute_dtype, gemm, shadow_of
+
+DEFAULT_CHUNK_ROWS = 8192
+
+
+def ce_inplace(logits: torch.Tensor, targets: torch.Tensor, loss_rows: torch.Tensor, grad_scale: float):
+    R, V = logits.shape
+    _lib.call("nnb_ce_inplace", _lib.ptr(logits), _lib.ptr(targets), _lib.ptr(loss_rows), _lib.i64(R), _lib.i32(V),
+              _lib.i64(logits.stride(0)), _lib.f32(grad_scale), _lib.i32(_CODE[logits.dtype]), _lib.vp(_lib.stream_ptr()))
+
+
+def linear_ce_fwd(x16, w16, targets, chunk_rows, dW_out):
+    """Returns (sum of row losses [fp32 scalar], dx [N, D] 16-bit for the MEAN loss); accumulates the
+    mean-loss weight gradient into dW_out (fp32 [V, D])."""
+    N, D = x16.shape
+    V = w16.shape[0]
+    chunk_rows = min(chunk_rows, N)
+    dx = torch.empty_like(x16)
+    loss_rows = torch.empty(N, dtype=torch.float32, device=x16.device)
+    logits = torch.empty((chunk_rows, V), dtype=x16.dtype, device=x16.device)
+    for r0 in range(0, N, chunk_rows):
+        r1 = min(r0 + chunk_rows, N)
+        lg = logits[: r1 - r0]
+        xc = x16[r0:r1]
+        gemm(xc, w16, out=lg)
+        ce_inplace(lg, targets[r0:r1], loss_rows[r0:r1], 1.0 / N)
+        gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=128)
+        gemm(lg, xc, a_mn=True, b_mn=True, out=dW_out, accumulate=True)
+    return loss_rows.sum(), dx
+
+
+class _LinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, targets, chunk_rows):
+        dt = compute_dtype()
+        w16 = shadow_of(weight, dt)
+        x16 = x if x.dtype == dt else x.to(dt)
+        x16 = x16 if x16.is_contiguous() else x16.contiguous()
+        tg = targets if targets.dtype == torch.int64 else targets.long()
+        tg = tg if tg.is_contiguous() else tg.contiguous()
+        need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+        dW = torch.zeros(weight.shape, dtype=torch.float32, device=x.device)
+        loss_sum, dx = linear_ce_fwd(x16, w16, tg, chunk_rows or DEFAULT_CHUNK_ROWS, dW)
+        ctx.save_for_backward(dx, dW, weight)
+        ctx.x_dtype = x.dtype
+        return loss_sum / x.shape[0]
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dx, dW, weight = ctx.saved_tensors
+        gx = (dx * dloss.to(dx.dtype)).to(ctx.x_dtype) if ctx.needs_input_grad[0] else None
+        gw = None
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "_main_grad", None)
+            if main is not None and main.dtype == torch.float32:
+                main.add_(dW * dloss)  # readiness of the tied weight is reported by the embedding backward
+            else:
+                gw = (dW * dloss).to(weight.dtype)
+        return gx, gw, None, None
+
+
+def linear_cross_entropy(x, weight, targets, chunk_rows=None):
+    """x: [N, D]; weight: [V, D] (fp32 master or 16-bit); targets: [N] int64 -> scalar mean loss (fp32)."""
+    return _LinearCE.apply(x, weight, targets, chunk_rows)

@@ -93,9 +93,9 @@ class _AddRMSNorm(torch.autograd.Function):
         h, rstd, weight = ctx.saved_tensors
         if dy is None:
             dy = torch.zeros(h.shape, dtype=_y_dtype(h, None) if ctx.delta_dtype is None else ctx.delta_dtype, device=h.device)
-        main = getattr(weight, "_flat_store", None)
-        if main is not None and weight.grad is not None and weight.grad.dtype == torch.float32:
-            dx, ddelta, _ = bwd(dy, h, rstd, weight, dh, ctx.delta_dtype, dw_out=weight.grad, accumulate=True)
+        main = getattr(weight, "_main_grad", None)
+        if main is not None and main.dtype == torch.float32:
+            dx, ddelta, _ = bwd(dy, h, rstd, weight, dh, ctx.delta_dtype, dw_out=main, accumulate=True)
             cb = getattr(weight, "_grad_ready_cb", None)
             if cb is not None:
                 cb(weight, True)

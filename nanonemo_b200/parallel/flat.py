@@ -49,6 +49,7 @@ class FlatParams:
             self.master[o:o + n].copy_(p.detach().reshape(-1))
             p.data = self.master[o:o + n].view(p.shape)
             p.grad = self.grad[o:o + n].view(p.shape)
+            p._main_grad = p.grad  # where the sm100 backward kernels accumulate directly
             p._flat_store, p._flat_offset = self, o
             if self.shadow is not None:
                 p._shadow = self.shadow[o:o + n].view(p.shape)

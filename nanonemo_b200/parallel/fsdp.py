@@ -1,0 +1,365 @@
+"""Fully sharded data parallel (ZeRO-3) on flat per-unit buffers.
+
+Same unit structure and knobs as the reference's FSDP2 wrapper (nanonemo/distributed/fsdp.py:21-38):
+one unit per transformer block plus a root unit (embedding + final norm); parameters are
+all-gathered before a unit's forward and again before its backward when ``reshard_after_forward``
+is set; gradients are reduce-scattered in fp32 only on the last micro-batch of a step
+(``sync_ctx(last)``); optional explicit prefetch of the next unit (forward) / previous unit
+(backward); ``param_dtype`` selects the dtype of the gathered parameters (fp32, or a 16-bit dtype,
+in which case the 16-bit shards are what crosses NVLink).
+
+What is different is the machinery. Every unit is a range of four flat buffers:
+  * ``full``      gathered parameters (param_dtype); ``p.data`` of the unit's parameters are views;
+  * ``grad``      fp32 unsharded gradients, in symmetric memory; ``p.grad`` are views;
+  * ``shard``     this rank's 1/world slice of fp32 master weights, and AdamW moments ``m``, ``v``;
+  * ``wire``      this rank's slice in param_dtype, in symmetric memory: the source of all-gathers.
+With ``comm="fused"`` the all-gather is a pull kernel over peer pointers on a side stream, the
+reduce-scatter kernel sums the peers' slices, applies 1/world and accumulates the shard's squared
+norm in the same pass, and the sharded AdamW (one launch for all units) clips with the global norm,
+updates the master shard and rewrites the wire shard. Otherwise torch.distributed collectives are
+used (NCCL; on gloo the reduce-scatter is an all-reduce + slice).
+
+Checkpoints gather full tensors (``state_for_checkpoint``) so they load under any layout.
+"""
+
+from contextlib import nullcontext
+
+import torch
+import torch.distributed as dist
+
+from nanonemo_b200.parallel.flat import ALIGN, _round_up
+from nanonemo_b200.parallel.strategy import LocalStrategy
+
+_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+class Unit:
+    def __init__(self, name, modules, params, names):
+        self.name, self.modules, self.params, self.names = name, modules, params, names
+        self.lo = self.hi = 0          # range in the full flat buffers
+        self.offsets = []              # per-parameter offset inside the unit
+        self.gathered = False
+        self.gather_event = None
+        self.pending = 0
+
+
+class FSDPStrategy(LocalStrategy):
+    name = "fsdp"
+    sharded_grads = True
+
+    def __init__(self, model, d, param_dtype="fp32", reshard_after_forward=True, prefetch=False, comm="auto",
+                 group=None, step_model=None, precision="fp32"):
+        super().__init__(model, None, step_model)
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.dp_rank, self.dp_world = self.rank, self.world
+        self.device = torch.device(d.device)
+        self.cuda = self.device.type == "cuda"
+        self.param_dtype = _DT[param_dtype]
+        self.reshard, self.prefetch = reshard_after_forward, prefetch
+        self._sync = True
+        self._backward_phase = False
+        from nanonemo_b200.parallel.symm import fused_available
+
+        self.fused = fused_available(d, comm)
+        self._build_units()
+        self._allocate()
+        self._install_hooks()
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self.sumsq = torch.zeros((), dtype=torch.float32, device=self.device)
+        self._rs_done = []
+        self.gather_all(initial=True)
+
+    # ------------------------------------------------------------------ layout
+    def _build_units(self):
+        m = self.model
+        root_params = [("tok_emb.weight", m.tok_emb.weight), ("norm_out.weight", m.norm_out.weight)]
+        self.units = [Unit("root", [m], [p for _, p in root_params], [n for n, _ in root_params])]
+        for i, block in enumerate(m.blocks):
+            named = list(block.named_parameters())
+            self.units.append(Unit(f"blocks.{i}", [block], [p for _, p in named], [f"blocks.{i}.{n}" for n, _ in named]))
+        off = 0
+        for u in self.units:
+            u.lo, o = off, 0
+            for p in u.params:
+                u.offsets.append(o)
+                o += _round_up(p.numel(), ALIGN)
+            off += _round_up(o, ALIGN * self.world)
+            u.hi = off
+        self.numel = off
+        self.shard_numel = off // self.world
+
+    def _shard_range(self, u):
+        """Range of unit u inside this rank's shard buffers."""
+        return u.lo // self.world, u.hi // self.world
+
+    def _allocate(self):
+        dev, W = self.device, self.world
+        self.full = torch.zeros(self.numel, dtype=self.param_dtype, device=dev)
+        self.symm_grad = self.symm_wire = None
+        if self.fused:
+            from nanonemo_b200.parallel.symm import SymmetricBuffer, SymmetricComm
+
+            self.symm_grad = SymmetricBuffer(self.numel, torch.float32, dev, self.group)
+            self.grad = self.symm_grad.tensor
+            self.symm_wire = SymmetricBuffer(self.shard_numel, self.param_dtype, dev, self.group)
+            self.wire = self.symm_wire.tensor
+            self.comm = SymmetricComm(dev, self.group, self.rank, self.world)
+        else:
+            self.grad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
+            self.wire = torch.zeros(self.shard_numel, dtype=self.param_dtype, device=dev)
+        self.grad.zero_()
+        self.shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=dev)
+        self.shard_grad = torch.zeros(self.shard_numel, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros_like(self.shard)
+        self.exp_avg_sq = torch.zeros_like(self.shard)
+        self.decay_flags = torch.zeros(self.shard_numel // ALIGN, dtype=torch.uint8, device=dev)
+        self.opt_step = 0
+        # scatter the initial full weights into the shards (every rank initialised identically)
+        with torch.no_grad():
+            for u in self.units:
+                tmp = torch.zeros(u.hi - u.lo, dtype=torch.float32, device=dev)
+                for p, o in zip(u.params, u.offsets):
+                    tmp[o:o + p.numel()].copy_(p.detach().reshape(-1))
+                per = (u.hi - u.lo) // W
+                s0, s1 = self._shard_range(u)
+                self.shard[s0:s1].copy_(tmp[self.rank * per:(self.rank + 1) * per])
+                for p, o in zip(u.params, u.offsets):
+                    n = p.numel()
+                    p.data = self.full[u.lo + o:u.lo + o + n].view(p.shape)
+                    if self.param_dtype == torch.float32:
+                        p.grad = self.grad[u.lo + o:u.lo + o + n].view(p.shape)
+                    p._main_grad = self.grad[u.lo + o:u.lo + o + n].view(p.shape)
+                    if self.param_dtype != torch.float32:
+                        p._shadow = p.data
+            self.wire.copy_(self.shard)
+
+    def set_weight_decay(self, opt):
+        """Mark which 256-element blocks of the shard get weight decay (from the optimizer's groups)."""
+        decay_ids = {id(p) for g in opt.param_groups if g["weight_decay"] != 0.0 for p in g["params"]}
+        self._wd = max(g["weight_decay"] for g in opt.param_groups)
+        full_flags = torch.zeros(self.numel // ALIGN, dtype=torch.uint8, device=self.device)
+        for u in self.units:
+            for p, o in zip(u.params, u.offsets):
+                if id(p) in decay_ids:
+                    a = (u.lo + o) // ALIGN
+                    full_flags[a:a + _round_up(p.numel(), ALIGN) // ALIGN] = 1
+        for u in self.units:
+            per = (u.hi - u.lo) // self.world // ALIGN
+            a = u.lo // ALIGN + self.rank * per
+            s0 = u.lo // self.world // ALIGN
+            self.decay_flags[s0:s0 + per] = full_flags[a:a + per]
+        self._opt = opt
+
+    # ------------------------------------------------------------------ collectives
+    def _gather(self, u, initial=False):
+        """Bring unit u's parameters from the wire shards of all ranks into `full`."""
+        s0, s1 = self._shard_range(u)
+        per = s1 - s0
+        dst = self.full[u.lo:u.hi]
+        if self.fused and not initial:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.all_gather(self.symm_wire, dst, s0 * self.wire.element_size(), per * self.wire.element_size())
+                done = torch.cuda.Event()
+                done.record()
+            u.gather_event = done
+            self.launches += 1
+        elif self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                dist.all_gather_into_tensor(dst, self.wire[s0:s1].contiguous(), group=self.group)
+                done = torch.cuda.Event()
+                done.record()
+            u.gather_event = done
+        else:
+            dist.all_gather_into_tensor(dst, self.wire[s0:s1].contiguous(), group=self.group)
+        u.gathered = True
+
+    def _wait_gather(self, u):
+        if not u.gathered:
+            self._gather(u)
+        if u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+            u.gather_event = None
+
+    def gather_all(self, initial=False):
+        for u in self.units:
+            self._gather(u, initial)
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            for u in self.units:
+                u.gather_event = None
+
+    def _reduce_scatter(self, u):
+        s0, s1 = self._shard_range(u)
+        per = s1 - s0
+        out = self.shard_grad[s0:s1]
+        if self.fused:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.reduce_scatter(self.symm_grad, out, self.sumsq, u.lo, per, 1.0 / self.world)
+            self.launches += 1
+        elif self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                dist.reduce_scatter_tensor(out, self.grad[u.lo:u.hi], group=self.group)
+                out.mul_(1.0 / self.world)
+        else:
+            g = self.grad[u.lo:u.hi]
+            dist.all_reduce(g, group=self.group)  # gloo has no reduce-scatter
+            out.copy_(g[self.rank * per:(self.rank + 1) * per]).mul_(1.0 / self.world)
+        self._rs_done.append(u)
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self):
+        units = self.units
+        for i, u in enumerate(units):
+            if i == 0:
+                continue  # the root is gathered at step start and kept through forward and backward
+            block = u.modules[0]
+            block.register_forward_pre_hook(lambda mod, args, i=i: self._pre_forward(i))
+            block.register_forward_hook(lambda mod, args, out, i=i: self._post_forward(i))
+            block.register_full_backward_pre_hook(lambda mod, gout, i=i: self._pre_backward(i))
+        for u in units:
+            for p in u.params:
+                p.register_post_accumulate_grad_hook(lambda p, u=u: self._on_grad(u, p, False))
+                p._grad_ready_cb = lambda p, manual=True, u=u: self._on_grad(u, p, manual)
+
+    def _pre_forward(self, i):
+        self._wait_gather(self.units[i])
+        if self.prefetch and i + 1 < len(self.units) and not self.units[i + 1].gathered:
+            self._gather(self.units[i + 1])
+
+    def _post_forward(self, i):
+        if self.reshard and torch.is_grad_enabled():
+            self.units[i].gathered = False  # the buffer stays allocated; the next use gathers again
+
+    def _pre_backward(self, i):
+        self._wait_gather(self.units[i])
+        if self.prefetch and i - 1 >= 1 and not self.units[i - 1].gathered:
+            self._gather(self.units[i - 1])
+
+    def _on_grad(self, u, p, manual):
+        if getattr(p, "_manual_ready", False) and not manual:
+            return
+        if p.grad is not None and p.grad.data_ptr() != p._main_grad.data_ptr():
+            p._main_grad.add_(p.grad)  # 16-bit gathered parameters: autograd produced a 16-bit grad
+            p.grad = None
+        u.pending -= 1
+        if u.pending == 0 and self._sync:
+            self._reduce_scatter(u)
+
+    # ------------------------------------------------------------------ strategy API
+    def sync_ctx(self, last: bool):
+        self._sync = last
+        for u in self.units:
+            u.pending = len(u.params)
+        if not self.units[0].gathered:
+            self._gather(self.units[0])
+        self._wait_gather(self.units[0])
+        if self.prefetch and not self.units[1].gathered:
+            self._gather(self.units[1])
+        return nullcontext()
+
+    def finish_grads(self):
+        for u in self.units:
+            if u not in self._rs_done:
+                self._reduce_scatter(u)
+        self._rs_done = []
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def step(self, opt, grad_clip, scaler=None, keep_grads=False):
+        assert scaler is None, "the sharded strategies run in bf16 / fp32 (no loss scaler)"
+        if not hasattr(self, "_opt"):
+            self.set_weight_decay(opt)
+        self.finish_grads()
+        if self.fused:
+            sumsq = self.sumsq.clone()
+        else:
+            sumsq = self.shard_grad.pow(2).sum()
+        dist.all_reduce(sumsq, group=self.group)
+        norm = sumsq.sqrt()
+        self.opt_step += 1
+        g0 = opt.param_groups[0]
+        if self.fused:
+            from nanonemo_b200.ops.adamw import adamw_flat
+
+            adamw_flat(self.shard, self.shard_grad, self.exp_avg, self.exp_avg_sq,
+                       self.wire if self.param_dtype != torch.float32 else None, self.decay_flags, lr=g0["lr"],
+                       beta1=g0["betas"][0], beta2=g0["betas"][1], eps=g0["eps"], weight_decay=self._wd,
+                       step=self.opt_step, grad_norm_sq=sumsq, max_norm=grad_clip, zero_grad=False)
+            if self.param_dtype == torch.float32:
+                self.wire.copy_(self.shard)
+            self.launches += 1
+        else:
+            coef = (grad_clip / (norm + 1e-6)).clamp(max=1.0)
+            g = self.shard_grad * coef
+            b1, b2 = g0["betas"]
+            decay = self.decay_flags.repeat_interleave(ALIGN).to(torch.float32) * (g0["lr"] * self._wd)
+            self.shard.mul_(1.0 - decay)
+            self.exp_avg.lerp_(g, 1 - b1)
+            self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+            bc1, bc2 = 1 - b1 ** self.opt_step, 1 - b2 ** self.opt_step
+            denom = (self.exp_avg_sq.sqrt() / (bc2 ** 0.5)).add_(g0["eps"])
+            self.shard.addcdiv_(self.exp_avg, denom, value=-g0["lr"] / bc1)
+            self.wire.copy_(self.shard)
+        self.grad.zero_()
+        self.sumsq.zero_()
+        for u in self.units:
+            u.gathered = False
+        # the root and (with prefetch) the first block are needed at once: start gathering now
+        self._gather(self.units[0])
+        return norm
+
+    # ------------------------------------------------------------------ checkpoint state (full tensors)
+    def _full_from_shards(self, shard_buf):
+        out = {}
+        for u in self.units:
+            s0, s1 = self._shard_range(u)
+            full = torch.empty(u.hi - u.lo, dtype=shard_buf.dtype, device=self.device)
+            dist.all_gather_into_tensor(full, shard_buf[s0:s1].contiguous(), group=self.group)
+            for n, p, o in zip(u.names, u.params, u.offsets):
+                out[n] = full[o:o + p.numel()].view(p.shape).clone()
+        return out
+
+    def state_for_checkpoint(self, opt):
+        return {"model": self._full_from_shards(self.shard),
+                "optim": {"exp_avg": self._full_from_shards(self.exp_avg),
+                          "exp_avg_sq": self._full_from_shards(self.exp_avg_sq),
+                          "step": torch.tensor(float(self.opt_step))}}
+
+    def load_from_checkpoint(self, opt, state):
+        with torch.no_grad():
+            for key, buf in (("model", self.shard), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+                src = state["model"] if key == "model" else state["optim"][key]
+                for u in self.units:
+                    tmp = torch.zeros(u.hi - u.lo, dtype=torch.float32, device=self.device)
+                    for n, p, o in zip(u.names, u.params, u.offsets):
+                        tmp[o:o + p.numel()].copy_(src[n].reshape(-1))
+                    per = (u.hi - u.lo) // self.world
+                    s0, s1 = self._shard_range(u)
+                    buf[s0:s1].copy_(tmp[self.rank * per:(self.rank + 1) * per])
+            self.opt_step = int(float(state["optim"]["step"]))
+            self.wire.copy_(self.shard)
+        self.gather_all(initial=not self.fused)
+
+
+def build_fsdp(model_cfg, cfg, d):
+    from nanonemo_b200.train.trainer import build_model
+
+    model, step_model = build_model(model_cfg, cfg, d.device)
+    pd = cfg.fsdp_param_dtype
+    if pd == "fp32" and model_cfg.uses_sm100("linear_impl") and cfg.precision in ("bf16", "fp8"):
+        pd = "bf16"  # the tensor-core GEMMs consume 16-bit weights: gather them in that dtype
+    return FSDPStrategy(model, d, pd, cfg.fsdp_reshard_after_forward, cfg.fsdp_prefetch, cfg.comm,
+                        step_model=step_model, precision=cfg.precision)

@@ -80,3 +80,43 @@ class LocalStrategy:
 
     def scale_grads_(self, coef: torch.Tensor):
         self.store.grad.mul_(coef.to(self.store.grad.dtype))
+
+    # -- checkpoint state: layout-independent, full tensors keyed by parameter name
+    def named_full_params(self):
+        """(name, full fp32 tensor) for every parameter, the tied weight once."""
+        return [(n, p.detach()) for n, p in self.model.named_parameters()]
+
+    def state_for_checkpoint(self, opt) -> dict:
+        """{"model": {name: tensor}, "optim": {"exp_avg": {...}, "exp_avg_sq": {...}, "step": tensor}}.
+        Every strategy produces the same names and FULL shapes, so a checkpoint written under one
+        layout loads under any other."""
+        model, avg, avg_sq = {}, {}, {}
+        step = torch.zeros((), dtype=torch.float32)
+        by_param = {id(p): n for n, p in self.model.named_parameters()}
+        for n, p in self.model.named_parameters():
+            model[n] = p.detach()
+        for p, st in opt.state.items():
+            n = by_param.get(id(p))
+            if n is None or not st:
+                continue
+            avg[n], avg_sq[n] = st["exp_avg"], st["exp_avg_sq"]
+            step = torch.as_tensor(st["step"], dtype=torch.float32).detach().cpu().reshape(())
+        for n, p in self.model.named_parameters():  # a load target exists even before the first step
+            avg.setdefault(n, torch.zeros_like(p))
+            avg_sq.setdefault(n, torch.zeros_like(p))
+        return {"model": model, "optim": {"exp_avg": avg, "exp_avg_sq": avg_sq, "step": step}}
+
+    def load_from_checkpoint(self, opt, state: dict) -> None:
+        step = float(state["optim"]["step"])
+        with torch.no_grad():
+            for n, p in self.model.named_parameters():
+                p.copy_(state["model"][n])
+                st = opt.state[p]
+                if "exp_avg" not in st:
+                    st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(p), torch.zeros_like(p)
+                st["exp_avg"].copy_(state["optim"]["exp_avg"][n])
+                st["exp_avg_sq"].copy_(state["optim"]["exp_avg_sq"][n])
+                st["step"] = torch.tensor(step, dtype=torch.float32)
+        if self.store is not None:
+            self.store.rebind_grads()
+            self.store.refresh_shadow()

@@ -7,9 +7,10 @@ On-disk layout (same as the reference, nanonemo/train/checkpoint.py:1-80):
 ``latest`` is written only after every rank's files are on disk (a barrier follows the save), so a
 save that was interrupted is never resumed from; the two newest checkpoints are kept.
 
-Every strategy exposes its state through ``strategy.state_for_checkpoint(opt)`` as plain names ->
-tensors (full tensors for replicated layouts, DTensor shards for sharded ones), so a checkpoint
-written under one layout loads under another: DCP reshards on load.
+Every strategy exposes its state through ``strategy.state_for_checkpoint(opt)`` as parameter names
+-> FULL tensors (sharded layouts gather their shards for the save; DCP writes a replicated tensor
+once), so a checkpoint written under one layout (say FSDP on 8 ranks) loads under any other (DDP on
+2, a single process, the HF exporter): each layout slices what it owns on load.
 """
 
 import json
@@ -20,30 +21,22 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
-from torch.distributed.checkpoint.state_dict import get_state_dict, set_state_dict
 
 
-def _model_of(obj):
-    return getattr(obj, "model", obj)
+def _as_strategy(obj):
+    if hasattr(obj, "state_for_checkpoint"):
+        return obj
+    from nanonemo_b200.parallel.strategy import LocalStrategy
+
+    return LocalStrategy(obj)  # a bare module
 
 
 def _state(obj, opt) -> dict:
-    if hasattr(obj, "state_for_checkpoint"):
-        return obj.state_for_checkpoint(opt)
-    msd, osd = get_state_dict(_model_of(obj), opt)  # also materialises empty optimizer state as a load target
-    return {"model": msd, "optim": osd}
+    return _as_strategy(obj).state_for_checkpoint(opt)
 
 
 def _restore(obj, opt, state) -> None:
-    if hasattr(obj, "load_from_checkpoint"):
-        obj.load_from_checkpoint(opt, state)
-        return
-    set_state_dict(_model_of(obj), opt, model_state_dict=state["model"], optim_state_dict=state["optim"])
-    store = getattr(obj, "store", None)
-    if store is not None:
-        store.rebind_optimizer_state(opt)
-        store.rebind_grads()
-        store.refresh_shadow()
+    _as_strategy(obj).load_from_checkpoint(opt, state)
 
 
 class Checkpointer:

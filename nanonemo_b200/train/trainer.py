@@ -127,9 +127,10 @@ def build_scaler(cfg: TrainConfig, device: str, sharded: bool = False):
 
 
 def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, grad_clip: float,
-               amp_dtype=None, scaler=None, keep_grads: bool = False):
+               amp_dtype=None, scaler=None, keep_grads: bool = False, host_sync: bool = True):
     """One optimizer step over `accum` micro-batches -> (mean loss over ranks, pre-clip grad norm),
-    both floats, fetched with a single device->host copy."""
+    both floats, fetched with a single device->host copy. With host_sync=False the pair is returned
+    as one 2-element device tensor and nothing waits for the GPU."""
     model = strategy.step_model
     loss_sum = None
     for i in range(accum):
@@ -143,6 +144,8 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
         loss_sum = loss if loss_sum is None else loss_sum + loss
     grad_norm = strategy.step(opt, grad_clip, scaler, keep_grads)
     both = torch.stack((parallel.all_mean(loss_sum.float()).reshape(()), grad_norm.float().reshape(())))
+    if not host_sync:
+        return both
     loss_f, norm_f = both.tolist()  # the only host sync of the step
     return loss_f, norm_f
 
