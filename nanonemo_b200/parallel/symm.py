@@ -17,7 +17,6 @@ import os
 import torch
 import torch.distributed as dist
 
-FLAG_WORDS = 1 << 16  # uint32 flags per rank (phase x block x peer slots)
 STATUS_WORDS = 8
 
 
@@ -47,36 +46,73 @@ class SymmetricBuffer:
         self.ptr_array = (ctypes.c_void_p * 16)(*self.peer_ptrs)
 
 
+class SymmetricComm:
+    """Launcher of the collective kernels (csrc/comm.cu) for one group: owns the symmetric flag
+    buffer, the epoch counter and the status words the kernels write when a bounded wait runs out."""
+
+    def __init__(self, device, group, rank: int, world: int, blocks: int | None = None):
+        from nanonemo_b200.ops import _lib
+
+        self.rank, self.world, self.group = rank, world, group
+        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", "32"))
+        words = _lib.lib().nnb_comm_flag_words(self.blocks)
+        self.flags = SymmetricBuffer(words, torch.int32, device, group)
+        self.flags.tensor.zero_()
+        self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def _next(self):
+        self.epoch += 1
+        return self.epoch
+
+    def all_reduce_(self, data: "SymmetricBuffer", lo: int, hi: int, scale: float, multimem: bool = False):
+        from nanonemo_b200.ops import _lib
+
+        _lib.call("nnb_allreduce_f32", data.ptr_array, self.flags.ptr_array,
+                  ctypes.c_void_p(data.multicast_ptr if multimem else 0), _lib.ptr(self.status), _lib.i32(self.rank),
+                  _lib.i32(self.world), _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale), _lib.i32(self._next()),
+                  _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+
+    def reduce_scatter(self, data: "SymmetricBuffer", out: torch.Tensor, sumsq: torch.Tensor | None, lo: int, per: int,
+                       scale: float):
+        """out[i] = scale * sum over ranks of data[lo + rank * per + i]; sumsq += sum(out ** 2)."""
+        from nanonemo_b200.ops import _lib
+
+        _lib.call("nnb_reduce_scatter_f32", data.ptr_array, self.flags.ptr_array, _lib.ptr(out), _lib.ptr(sumsq),
+                  _lib.ptr(self.status), _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo), _lib.i64(per),
+                  _lib.f32(scale), _lib.i32(self._next()), _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+
+    def all_gather(self, shards: "SymmetricBuffer", full: torch.Tensor, src_off_bytes: int, per_bytes: int):
+        """full[r * per : (r + 1) * per] = rank r's bytes [src_off, src_off + per) of `shards`."""
+        from nanonemo_b200.ops import _lib
+
+        _lib.call("nnb_allgather_bytes", shards.ptr_array, self.flags.ptr_array, _lib.ptr(full), _lib.ptr(self.status),
+                  _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(src_off_bytes), _lib.i64(per_bytes),
+                  _lib.i32(self._next()), _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+
+    def check_status(self):
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            raise RuntimeError(f"fused collective gave up waiting: code={st[0]} rank={st[1]} peer={st[2]} "
+                               f"block={st[3]} epoch={st[4]}")
+
+
 class SymmetricAllReduce:
     """In-place two-shot all-reduce (+ scale) over ranges of one symmetric fp32 buffer."""
 
     def __init__(self, data: SymmetricBuffer, group=None):
         self.data = data
-        dev = data.tensor.device
-        self.flags = SymmetricBuffer(FLAG_WORDS, torch.int32, dev, group)
-        self.flags.tensor.zero_()
-        self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=dev)
-        self.epoch = 0
-        self.blocks = int(os.environ.get("NANONEMO_COMM_BLOCKS", "32"))
+        self.comm = SymmetricComm(data.tensor.device, group, data.rank, data.world)
         self.use_multimem = bool(data.multicast_ptr) and os.environ.get("NANONEMO_MULTIMEM", "0") == "1"
-        torch.cuda.synchronize(dev)
-        dist.barrier(group)
 
     def all_reduce_(self, lo: int, hi: int, scale: float):
-        from nanonemo_b200.ops import _lib
-
-        self.epoch += 1
-        _lib.call("nnb_allreduce_f32", self.data.ptr_array, self.flags.ptr_array,
-                  ctypes.c_void_p(self.data.multicast_ptr if self.use_multimem else 0),
-                  _lib.ptr(self.status), _lib.i32(self.data.rank), _lib.i32(self.data.world),
-                  _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale), _lib.i32(self.epoch), _lib.i32(self.blocks),
-                  ctypes.c_void_p(_lib.stream_ptr()))
+        self.comm.all_reduce_(self.data, lo, hi, scale, self.use_multimem)
 
     def check_status(self):
-        st = self.status.tolist()
-        if st[0] != 0:
-            raise RuntimeError(f"fused collective gave up waiting: code={st[0]} rank={st[1]} peer={st[2]} "
-                               f"block={st[3]} epoch={st[4]}")
+        self.comm.check_status()
 
 
 def make_grad_allreduce(d, comm: str, group=None):
