@@ -90,12 +90,21 @@ class Attention(nn.Module):
         self.wqkv = make_linear(cfg, cfg.d_model, self.q_dim + 2 * self.kv_dim)
         self.wo = make_linear(cfg, self.q_dim, cfg.d_model)
         self.rope_impl, self.attn_impl = r.rope_kernel, r.attn_kernel
+        self.tp = None  # parallel.tp.TPContext once the model has been sharded
 
     def split_qkv(self):
         """(wq, wk, wv) views of the fused projection weight."""
         return self.wqkv.weight.split((self.q_dim, self.kv_dim, self.kv_dim), dim=0)
 
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            # sequence parallel: x holds 1/tp of the tokens; gather them, attend over the local heads,
+            # and reduce-scatter the row-parallel projection's partial sums back to token shards
+            full = self.tp.gather_tokens(x).view(self.tp.B, self.tp.T, -1)
+            return self.tp.scatter_tokens(self._attend(full, cos, sin).reshape(-1, x.shape[-1]))
+        return self._attend(x, cos, sin)
+
+    def _attend(self, x, cos, sin):
         B, T, _ = x.shape
         H, KVH, hd = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self.wqkv(x)  # (B, T, (H + 2 KVH) hd)
@@ -128,11 +137,15 @@ class MLP(nn.Module):
         self.w_gu = make_linear(cfg, cfg.d_model, 2 * cfg.d_ff)  # rows [0, d_ff) = gate, [d_ff, 2 d_ff) = up
         self.w_down = make_linear(cfg, cfg.d_ff, cfg.d_model)
         self.act_impl = r.swiglu_kernel
+        self.tp = None
 
     def split_gu(self):
         return self.w_gu.weight.split((self.d_ff, self.d_ff), dim=0)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            full = self.tp.gather_tokens(x)
+            return self.tp.scatter_tokens(self.w_down(ops.swiglu_packed(self.w_gu(full), impl=self.act_impl)))
         return self.w_down(ops.swiglu_packed(self.w_gu(x), impl=self.act_impl))
 
 

@@ -27,6 +27,7 @@ class NanoNemo(nn.Module):
         self.lm_head = Linear(cfg.d_model, cfg.vocab_size, "sm100" if cfg.uses_sm100("linear_impl") else "torch")
         self.lm_head.weight = self.tok_emb.weight  # tied input/output embedding
         self.loss_impl, self.embed_impl = r.loss_kernel, r.embed_kernel
+        self.tp, self.vocab_start = None, 0  # set by parallel.tp.shard_model_
 
         cos, sin = rope_cache(cfg.head_dim, cfg.max_seq_len, cfg.rope_base)
         self.register_buffer("rope_cos", cos, persistent=False)
@@ -68,6 +69,8 @@ class NanoNemo(nn.Module):
         `loss_scale` is only a hint for the fused loss (it lets it pre-scale its gradients)."""
         T = idx.shape[1]
         assert T <= self.cfg.max_seq_len, f"sequence length {T} > max_seq_len {self.cfg.max_seq_len}"
+        if self.tp is not None:
+            return self._forward_tp(idx, targets)
         x, delta = ops.embedding(idx, self.tok_emb.weight, impl=self.embed_impl), None
         for block in self.blocks:
             x, delta = block(x, self.rope_cos, self.rope_sin, delta)
@@ -80,6 +83,24 @@ class NanoNemo(nn.Module):
         if targets is not None:
             loss = F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
         return logits, loss
+
+    def _forward_tp(self, idx, targets):
+        """Tensor + sequence parallel forward: token-sharded residual stream, vocabulary-sharded head."""
+        from nanonemo_b200.parallel.tp import _VocabParallelCE, _VocabParallelEmbedding
+
+        tp = self.tp
+        tp.B, tp.T = idx.shape
+        assert idx.numel() % tp.world == 0, "B * T must divide evenly over the tensor-parallel ranks"
+        out_dtype = getattr(self, "residual_dtype", torch.float32) if self.embed_impl == "sm100" else self.tok_emb.weight.dtype
+        x = _VocabParallelEmbedding.apply(idx.reshape(-1), self.tok_emb.weight, tp, self.vocab_start, out_dtype)
+        delta = None
+        for block in self.blocks:
+            x, delta = block(x, self.rope_cos, self.rope_sin, delta)
+        h = tp.gather_tokens(self.norm_out(x, delta)[0])
+        logits = self.lm_head(h)  # [B*T, V / tp]
+        if targets is None:
+            return logits, None
+        return logits, _VocabParallelCE.apply(logits, targets.reshape(-1), tp, self.vocab_start)
 
     def num_params(self, non_embedding: bool = False) -> int:
         n = sum(p.numel() for p in self.parameters())  # the tied weight is yielded once

@@ -1,0 +1,287 @@
+"""Tensor parallel + sequence parallel (Megatron style) with vocab-parallel embedding and loss.
+
+Layout, as in the reference (nanonemo/distributed/tp.py:33-66): ``wqkv`` / ``w_gu`` are column
+parallel (each rank owns H/tp query heads, KVH/tp KV heads, d_ff/tp hidden units), ``wo`` /
+``w_down`` row parallel, the tied embedding / head is sharded over the vocabulary, norm weights are
+replicated; the residual stream, the norms and the residual adds hold 1/tp of the tokens per rank
+(sequence parallel), with an all-gather entering attention / MLP / head and a reduce-scatter leaving
+``wo`` / ``w_down``; the loss is computed on vocabulary shards (three small all-reduces: row max,
+sum-exp, target logit) so full logits are never gathered.
+
+Differences: the model is built from the same seed as a single-process model and then SLICED
+(``shard_model_``), so initial weights match exactly; tokens are partitioned as contiguous chunks of
+the flattened (B*T) token axis, which makes every gather / scatter a contiguous copy; the local
+parameters live in a ``FlatParams`` store so clipping and AdamW are the fused flat kernels; and the
+operators on local tensors (norm, RoPE, attention, SwiGLU, GEMMs) are the same sm100 kernels as on
+one GPU — the reference has to force its ``torch`` norms and loss under TP (tp.py:37-38).
+With ``comm="fused"`` the all-gather / reduce-scatter of activations run as this framework's
+peer-pointer kernels over symmetric staging buffers; otherwise torch.distributed is used.
+"""
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from nanonemo_b200.parallel.strategy import LocalStrategy
+
+
+# ----------------------------------------------------------------------------- collectives with autograd
+class TPContext:
+    def __init__(self, group, rank: int, world: int, device, fused_comm=None):
+        self.group, self.rank, self.world, self.device = group, rank, world, torch.device(device)
+        self.fused = fused_comm  # ActivationComm (symmetric staging + kernels) or None
+        self.B = self.T = 0
+        self.gloo = self.device.type != "cuda"
+
+    # raw collectives on contiguous 2-D tensors, along dim 0
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.contiguous()
+        if self.fused is not None:
+            return self.fused.all_gather(x)
+        out = torch.empty((x.shape[0] * self.world, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=self.group)
+        return out
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.contiguous()
+        n = x.shape[0] // self.world
+        if self.fused is not None and x.dtype in (torch.float32,):
+            return self.fused.reduce_scatter(x)
+        if self.gloo:
+            x = x.clone()
+            dist.all_reduce(x, group=self.group)
+            return x[self.rank * n:(self.rank + 1) * n].clone()
+        out = torch.empty((n, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=self.group)
+        return out
+
+    def all_reduce(self, x: torch.Tensor, op=dist.ReduceOp.SUM) -> torch.Tensor:
+        dist.all_reduce(x, op=op, group=self.group)
+        return x
+
+    # differentiable forms
+    def gather_tokens(self, x):
+        return _Gather.apply(x, self)
+
+    def scatter_tokens(self, x):
+        return _ReduceScatter.apply(x, self)
+
+
+class _Gather(torch.autograd.Function):
+    """all-gather along tokens; backward is the reduce-scatter of the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.all_gather(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.reduce_scatter(g), None
+
+
+class _ReduceScatter(torch.autograd.Function):
+    """reduce-scatter along tokens; backward is the all-gather of the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.reduce_scatter(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_gather(g), None
+
+
+class _VocabParallelEmbedding(torch.autograd.Function):
+    """Rows of the vocabulary shard this rank owns, zeros elsewhere, summed and scattered over tokens."""
+
+    @staticmethod
+    def forward(ctx, idx_flat, weight, tp, v0, out_dtype):
+        V = weight.shape[0]
+        local = idx_flat - v0
+        mine = (local >= 0) & (local < V)
+        rows = F.embedding(local.clamp(0, V - 1), weight).to(out_dtype)
+        rows = rows * mine.unsqueeze(-1).to(rows.dtype)
+        ctx.save_for_backward(local, mine, weight)
+        ctx.tp = tp
+        return tp.reduce_scatter(rows)
+
+    @staticmethod
+    def backward(ctx, g):
+        local, mine, weight = ctx.saved_tensors
+        g_full = ctx.tp.all_gather(g).float() * mine.unsqueeze(-1)
+        main = getattr(weight, "_main_grad", None)
+        target = main if main is not None and main.dtype == torch.float32 else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        target.index_add_(0, local.clamp(0, weight.shape[0] - 1), g_full)
+        if target is main:
+            cb = getattr(weight, "_grad_ready_cb", None)
+            if cb is not None:
+                cb(weight, True)
+            return None, None, None, None, None
+        return None, target.to(weight.dtype), None, None, None
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    """Mean cross entropy over vocabulary shards: logits_local [N, V/tp]; targets are global ids."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, tp, v0):
+        lf = logits.float()
+        m = tp.all_reduce(lf.max(dim=-1).values, dist.ReduceOp.MAX)
+        e = torch.exp(lf - m.unsqueeze(-1))
+        s = tp.all_reduce(e.sum(dim=-1))
+        local = targets - v0
+        mine = (local >= 0) & (local < lf.shape[1])
+        tl = lf.gather(1, local.clamp(0, lf.shape[1] - 1).unsqueeze(1)).squeeze(1) * mine
+        tl = tp.all_reduce(tl)
+        loss = (m + torch.log(s) - tl).mean()
+        ctx.save_for_backward(e, s, local, mine)
+        ctx.dtype = logits.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        e, s, local, mine = ctx.saved_tensors
+        N = e.shape[0]
+        grad = e / s.unsqueeze(-1)
+        rows = torch.arange(N, device=e.device)[mine]
+        grad[rows, local[mine]] -= 1.0
+        return (grad * (g / N)).to(ctx.dtype), None, None, None
+
+
+# ----------------------------------------------------------------------------- model surgery
+def check_divisible(cfg, tp: int):
+    if cfg.n_heads % tp or cfg.n_kv_heads % tp:
+        raise ValueError(f"tensor parallel degree {tp} must divide n_heads={cfg.n_heads} and n_kv_heads={cfg.n_kv_heads} "
+                         "(head-aligned split; 12 query / 4 KV heads allow tp in {1, 2, 4})")
+    if cfg.d_ff % tp or cfg.vocab_size % tp:
+        raise ValueError(f"tensor parallel degree {tp} must divide d_ff={cfg.d_ff} and vocab_size={cfg.vocab_size}")
+
+
+@torch.no_grad()
+def shard_model_(model, tp: TPContext):
+    """Slice a fully initialised model in place to this rank's tensor-parallel shard."""
+    cfg, r, W = model.cfg, tp.rank, tp.world
+    check_divisible(cfg, W)
+    hd = cfg.head_dim
+    Hl, KVl, Fl, Vl = cfg.n_heads // W, cfg.n_kv_heads // W, cfg.d_ff // W, cfg.vocab_size // W
+    for block in model.blocks:
+        a, m = block.attn, block.mlp
+        wq, wk, wv = a.split_qkv()
+        a.wqkv.weight.data = torch.cat((wq[r * Hl * hd:(r + 1) * Hl * hd], wk[r * KVl * hd:(r + 1) * KVl * hd],
+                                        wv[r * KVl * hd:(r + 1) * KVl * hd])).contiguous()
+        a.wo.weight.data = a.wo.weight[:, r * Hl * hd:(r + 1) * Hl * hd].contiguous()
+        a.n_heads, a.n_kv_heads, a.q_dim, a.kv_dim = Hl, KVl, Hl * hd, KVl * hd
+        wg, wu = m.split_gu()
+        m.w_gu.weight.data = torch.cat((wg[r * Fl:(r + 1) * Fl], wu[r * Fl:(r + 1) * Fl])).contiguous()
+        m.w_down.weight.data = m.w_down.weight[:, r * Fl:(r + 1) * Fl].contiguous()
+        m.d_ff = Fl
+        a.tp = m.tp = tp
+    model.tok_emb.weight.data = model.tok_emb.weight[r * Vl:(r + 1) * Vl].contiguous()
+    model.tp, model.vocab_start = tp, r * Vl
+    return model
+
+
+SHARD_DIMS = {"attn.wqkv.weight": "qkv", "attn.wo.weight": 1, "mlp.w_gu.weight": "gu", "mlp.w_down.weight": 1,
+              "tok_emb.weight": 0}
+
+
+def shard_rule(name: str):
+    for key, rule in SHARD_DIMS.items():
+        if name.endswith(key):
+            return rule
+    return None  # replicated (norm weights)
+
+
+class TPStrategy(LocalStrategy):
+    name = "tp"
+    sharded_grads = True
+
+    def __init__(self, model, tp: TPContext, store, step_model=None, dp_group=None):
+        super().__init__(model, store, step_model)
+        self.tp = tp
+        self.replicated = [p for n, p in model.named_parameters() if shard_rule(n) is None]
+        self.dp_rank, self.dp_world = 0, 1  # every TP rank reads the same batch: one data-parallel replica
+
+    def finish_grads(self):
+        # norm weights saw only this rank's tokens: sum their gradients over the TP group
+        if self.replicated:
+            flat = torch.cat([p._main_grad.reshape(-1) if hasattr(p, "_main_grad") else p.grad.reshape(-1) for p in self.replicated])
+            self.tp.all_reduce(flat)
+            o = 0
+            for p in self.replicated:
+                g = p._main_grad if hasattr(p, "_main_grad") else p.grad
+                g.copy_(flat[o:o + p.numel()].view(p.shape))
+                o += p.numel()
+
+    def global_sumsq(self):
+        total = self.store.grad_sumsq()
+        rep = sum((p._main_grad.float().pow(2).sum() for p in self.replicated), torch.zeros((), device=total.device))
+        sharded = self.tp.all_reduce((total - rep).reshape(1).clone()).reshape(())
+        return sharded + rep
+
+    # checkpoint state: gather the shards back to full tensors
+    def _full(self, name, local):
+        rule, tp, cfg = shard_rule(name), self.tp, self.model.cfg
+        if rule is None:
+            return local.detach().clone()
+        parts = [torch.empty_like(local) for _ in range(tp.world)]
+        dist.all_gather(parts, local.detach().contiguous(), group=tp.group)
+        hd, W = cfg.head_dim, tp.world
+        if rule == "qkv":
+            q, kv = cfg.n_heads // W * hd, cfg.n_kv_heads // W * hd
+            return torch.cat([p[:q] for p in parts] + [p[q:q + kv] for p in parts] + [p[q + kv:] for p in parts])
+        if rule == "gu":
+            f = cfg.d_ff // W
+            return torch.cat([p[:f] for p in parts] + [p[f:] for p in parts])
+        return torch.cat(parts, dim=rule)
+
+    def _local(self, name, full):
+        rule, tp, cfg = shard_rule(name), self.tp, self.model.cfg
+        if rule is None:
+            return full
+        r, W, hd = tp.rank, tp.world, cfg.head_dim
+        if rule == "qkv":
+            Q, KV = cfg.n_heads * hd, cfg.n_kv_heads * hd
+            q, kv = Q // W, KV // W
+            return torch.cat((full[r * q:(r + 1) * q], full[Q + r * kv:Q + (r + 1) * kv], full[Q + KV + r * kv:Q + KV + (r + 1) * kv]))
+        if rule == "gu":
+            Fd, f = cfg.d_ff, cfg.d_ff // W
+            return torch.cat((full[r * f:(r + 1) * f], full[Fd + r * f:Fd + (r + 1) * f]))
+        n = full.shape[rule] // W
+        return full.narrow(rule, r * n, n)
+
+    def state_for_checkpoint(self, opt):
+        base = super().state_for_checkpoint(opt)
+        out = {"model": {}, "optim": {"exp_avg": {}, "exp_avg_sq": {}, "step": base["optim"]["step"]}}
+        for n in base["model"]:
+            out["model"][n] = self._full(n, base["model"][n])
+            out["optim"]["exp_avg"][n] = self._full(n, base["optim"]["exp_avg"][n])
+            out["optim"]["exp_avg_sq"][n] = self._full(n, base["optim"]["exp_avg_sq"][n])
+        return out
+
+    def load_from_checkpoint(self, opt, state):
+        local = {"model": {}, "optim": {"exp_avg": {}, "exp_avg_sq": {}, "step": state["optim"]["step"]}}
+        for n in state["model"]:
+            local["model"][n] = self._local(n, state["model"][n])
+            local["optim"]["exp_avg"][n] = self._local(n, state["optim"]["exp_avg"][n])
+            local["optim"]["exp_avg_sq"][n] = self._local(n, state["optim"]["exp_avg_sq"][n])
+        super().load_from_checkpoint(opt, local)
+
+
+def build_tp(model_cfg, cfg, d):
+    from nanonemo_b200.parallel.flat import FlatParams
+    from nanonemo_b200.train.trainer import build_model, shadow_dtype
+
+    if cfg.parallel == "fsdp_tp":
+        raise NotImplementedError("the 2-D fsdp_tp mesh is not built yet")
+    world = dist.get_world_size()
+    tp_size = cfg.tp_size or world
+    if tp_size != world:
+        raise ValueError("parallel=tp uses the whole world as the tensor-parallel group (tp_size must equal world)")
+    tp = TPContext(dist.group.WORLD, dist.get_rank(), world, d.device)
+    model, step_model = build_model(model_cfg, cfg, d.device)
+    shard_model_(model, tp)
+    store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg))
+    return TPStrategy(model, tp, store, step_model)
