@@ -128,3 +128,36 @@ extern "C" int nnb_adamw_flat(void* p, void* g, void* m, void* v, void* shadow, 
   NNB_LAUNCH_OK("adamw_flat");
   return 0;
 }
+
+// ---------------------------------------------------------------- sum of squares without allocation
+#include "nnb_noalloc.h"
+
+// Scratch for nnb_sumsq_f32_noalloc: block partials followed by the ticket word. In host code this
+// name is only a handle for cudaGetSymbolAddress, never a device address to pass to a kernel.
+static __device__ __align__(256) float g_sumsq_noalloc_scratch[NNB_SUMSQ_NOALLOC_MAX_BLOCKS + 1];
+
+extern "C" int nnb_sumsq_f32_noalloc(const void* x, long long n, void* out, cudaStream_t st) {
+  constexpr int kMaxDevices = 64;
+  static float* scratch_of[kMaxDevices] = {nullptr};
+  NNB_REQUIRE(x != nullptr && out != nullptr, "sumsq_noalloc: null pointer");
+  NNB_REQUIRE(nnb_aligned16(x), "sumsq_noalloc: input must be 16-byte aligned");
+  NNB_REQUIRE(n >= 0 && n <= NNB_SUMSQ_NOALLOC_MAX_ELEMS, "sumsq_noalloc: n=%lld is outside [0, %lld]", n,
+              (long long)NNB_SUMSQ_NOALLOC_MAX_ELEMS);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  NNB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, "sumsq_noalloc: cudaGetDevice failed or device %d >= %d", dev, kMaxDevices);
+  if (scratch_of[dev] == nullptr) {  // once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sumsq_noalloc_scratch);
+    NNB_REQUIRE(e == cudaSuccess && p != nullptr, "sumsq_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    scratch_of[dev] = p;
+  }
+  float* scratch = scratch_of[dev];
+  const int blocks = min(nnb_sumsq_blocks(), NNB_SUMSQ_NOALLOC_MAX_BLOCKS);
+  // the array keeps whatever the last call left: the ticket word must start at zero
+  e = cudaMemsetAsync(scratch + blocks, 0, sizeof(unsigned), st);
+  NNB_REQUIRE(e == cudaSuccess, "sumsq_noalloc: clearing the ticket word failed: %s", cudaGetErrorString(e));
+  sumsq_kernel<<<blocks, 512, 0, st>>>(static_cast<const float*>(x), n, scratch, static_cast<float*>(out), 0);
+  NNB_LAUNCH_OK("sumsq_noalloc");
+  return 0;
+}
