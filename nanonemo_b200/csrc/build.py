@@ -37,7 +37,7 @@ def _stale(obj: Path, deps: list[Path]) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h"))
+    headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h")) + sorted(HERE.glob("*.inc"))
     objdir = HERE / "build"
     objdir.mkdir(exist_ok=True)
     jobs = []

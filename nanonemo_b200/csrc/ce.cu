@@ -1,19 +1,17 @@
 // Cross-entropy half of the fused linear + cross-entropy over the tied head.
 //
 // The head is processed in row chunks: logits_c = x_c W^T (tcgen05 GEMM, bf16 [R, V]) -> this kernel
-// -> dx_c = g W and dW += g^T x_c (tcgen05 GEMMs). The kernel makes ONE pass over the chunk's logits:
-// a block owns a row, holds it in registers as packed 16-bit pairs, reduces max and sum-exp in fp32,
-// writes loss_row = logsumexp - logit[target], and overwrites the row in place with
-// g = (softmax - onehot) * grad_scale. The [B*T, V] logits never exist (at the 114M shape they would
-// be 3.3 GB in bf16 plus 6.6 GB for the fp32 copy the unfused path makes).
-// Same contract as the reference's Triton kernel (nanonemo/kernels/triton/linear_ce.py:21-41), which
-// re-reads each row in 4096-wide blocks; here the row stays on chip between the two phases.
+// -> dx_c = g W and dW += g^T x_c (tcgen05 GEMMs). The kernel reads each logit from HBM once and
+// writes it once: a block owns a row, reduces max and sum-exp in fp32, writes
+// loss_row = logsumexp - logit[target], and overwrites the row in place with
+// g = (softmax - onehot) * grad_scale. Only 16-bit logits of one chunk exist, never the fp32 copy of
+// the full [B*T, V] matrix that the unfused path makes (6.6 GB at the 114M shape).
+// Same contract as the reference's Triton kernel (nanonemo/kernels/triton/linear_ce.py:21-41).
 #include "common.cuh"
 
 namespace {
 
-constexpr int kCeThreads = 512;
-constexpr int kMaxVec = 16;  // uint4 (8 x 16-bit) per thread: rows up to 512 * 16 * 8 = 65536 columns
+constexpr int kCeThreads = 256;
 
 template <typename T>
 __device__ __forceinline__ float2 unpack2(uint32_t w);
@@ -38,22 +36,15 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ float block_reduce(float v, float* s_buf, bool is_max) {
-  v = is_max ? warp_max(v) : warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();
-  if (lane == 0) s_buf[warp] = v;
-  __syncthreads();
-  float r = (lane < (int)(blockDim.x >> 5)) ? s_buf[lane] : (is_max ? -INFINITY : 0.f);
-  r = is_max ? warp_max(r) : warp_sum(r);
-  return r;
-}
-
+// One block per row, two sweeps. Sweep 1 reads the row from HBM and keeps a running (max, sum-exp)
+// per thread; sweep 2 re-reads it — a row is ~100 KB and a few hundred rows are in flight, far below
+// the 126 MB L2, so the second read does not reach HBM — and overwrites it with the gradient.
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
                                                                 float* __restrict__ loss_rows, int V, long long ld,
                                                                 float grad_scale) {
-  __shared__ float s_buf[kCeThreads / 32];
+  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+  constexpr float kLog2e = 1.4426950408889634f;
   const long long row = blockIdx.x;
   T* x = logits + row * ld;
   const int nvec = V >> 3;
@@ -61,56 +52,61 @@ __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ 
   const bool valid = tgt >= 0 && tgt < V;
   const float x_t = valid ? to_f32(x[tgt]) : 0.f;
 
-  uint4 regs[kMaxVec];
-  float m = -INFINITY;
+  float m = -INFINITY, s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+    float f[8];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      regs[i] = reinterpret_cast<const uint4*>(x)[v];
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&regs[i]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = unpack2<T>(w[k]);
-        m = fmaxf(m, fmaxf(f.x, f.y));
-      }
+    for (int k = 0; k < 4; ++k) {
+      const float2 t = unpack2<T>(w[k]);
+      f[2 * k] = t.x; f[2 * k + 1] = t.y;
     }
-  }
-  m = block_reduce(m, s_buf, true);
-  float s = 0.f;
-  constexpr float kLog2e = 1.4426950408889634f;
+    float lm = f[0];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&regs[i]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = unpack2<T>(w[k]);
-        s += exp2f((f.x - m) * kLog2e) + exp2f((f.y - m) * kLog2e);
-      }
+    for (int k = 1; k < 8; ++k) lm = fmaxf(lm, f[k]);
+    if (lm > m) {
+      s *= exp2f((m - lm) * kLog2e);
+      m = lm;
     }
+    const float mb = m * kLog2e;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += exp2f(f[k] * kLog2e - mb);
   }
-  s = block_reduce(s, s_buf, false);
-  const float lse = m + logf(s);
+  // combine (m, s) pairs: warp, then block
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mn) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mn) * kLog2e));
+    m = mn;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { s_m[warp] = m; s_s[warp] = s; }
+  __syncthreads();
+  float M = s_m[0];
+#pragma unroll
+  for (int i = 1; i < kCeThreads / 32; ++i) M = fmaxf(M, s_m[i]);
+  float S = 0.f;
+#pragma unroll
+  for (int i = 0; i < kCeThreads / 32; ++i) S += s_m[i] == -INFINITY ? 0.f : s_s[i] * exp2f((s_m[i] - M) * kLog2e);
+  const float lse = M + logf(S);
   if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
   const float gs = valid ? grad_scale : 0.f;  // ignored rows contribute no gradient
+  const float lb = lse * kLog2e;
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      uint32_t* w = reinterpret_cast<uint32_t*>(&regs[i]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = unpack2<T>(w[k]);
-        const int col = v * 8 + 2 * k;
-        float g0 = exp2f((f.x - lse) * kLog2e) * gs, g1 = exp2f((f.y - lse) * kLog2e) * gs;
-        if (col == tgt) g0 -= gs;
-        if (col + 1 == tgt) g1 -= gs;
-        w[k] = pack2<T>(g0, g1);
-      }
-      reinterpret_cast<uint4*>(x)[v] = regs[i];
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack2<T>(w[k]);
+      const int col = v * 8 + 2 * k;
+      float g0 = exp2f(f.x * kLog2e - lb) * gs, g1 = exp2f(f.y * kLog2e - lb) * gs;
+      if (col == tgt) g0 -= gs;
+      if (col + 1 == tgt) g1 -= gs;
+      w[k] = pack2<T>(g0, g1);
     }
+    reinterpret_cast<uint4*>(x)[v] = raw;
   }
 }
 
@@ -120,7 +116,7 @@ __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ 
 // targets: int64 [R] (out-of-range = ignored row); loss_rows: fp32 [R].
 extern "C" int nnb_ce_inplace(void* logits, const void* targets, void* loss_rows, long long R, int V, long long ld,
                               float grad_scale, int dtype, cudaStream_t st) {
-  NNB_REQUIRE(V % 8 == 0 && V <= kCeThreads * kMaxVec * 8, "ce: V=%d must be a multiple of 8 and <= %d", V, kCeThreads * kMaxVec * 8);
+  NNB_REQUIRE(V % 8 == 0 && V > 0, "ce: V=%d must be a positive multiple of 8", V);
   NNB_REQUIRE(ld % 8 == 0 && nnb_aligned16(logits), "ce: logits rows must be 16-byte aligned");
   if (R == 0) return 0;
   NNB_DISPATCH_16(dtype, T, {

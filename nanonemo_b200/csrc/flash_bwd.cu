@@ -14,7 +14,9 @@
 // MN-major (dK, dV) without any transposed copy. dQ partial tiles leave through a swizzled fp32
 // staging tile and a TMA reduce-add (cp.reduce.async.bulk.tensor .add.f32) into an fp32 buffer that a
 // small kernel converts at the end. D = rowsum(dO * O) is a pre-pass kernel in this file.
-// 192 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 compute. All waits are bounded.
+// 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 compute: two threads per query row,
+// one for keys 0..63 of the tile and one for keys 64..127 (same TMEM lanes, different columns), which
+// halves the latency of the softmax phase the tensor core has to wait for. All waits are bounded.
 #include "sm100.cuh"
 
 namespace {
@@ -22,7 +24,8 @@ namespace {
 using namespace sm100;
 
 constexpr int BQ = 128, BKV = 128, HD = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;           // TMA warp, MMA warp, 2 x 4 compute warps
+constexpr int kComputeThreads = 256;
 constexpr int kTile16 = 128 * 64 * 2;     // a [128 x 64] 16-bit tile = 16 KB
 constexpr int kStagesQ = 2;
 // shared memory map (bytes)
@@ -72,9 +75,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar_qe + 8 * s, 1);
     }
     mbar_init(bar_sdp, 1);
-    mbar_init(bar_pds, 128);
+    mbar_init(bar_pds, kComputeThreads);
     mbar_init(bar_dq, 1);
-    mbar_init(bar_dqr, 128);
+    mbar_init(bar_dqr, kComputeThreads);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -147,13 +150,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ compute warps (one thread per query row)
+    // ------------------------------------------------------------------ compute warps (two threads per query row)
+    const int half = (warp - 2) >> 2;          // 0: keys 0..63 / dQ columns 0..31 / dV; 1: keys 64..127 / dQ columns 32..63 / dK
     const int q = warp & 3, row = q * 32 + lane, sw = row & 7;
+    const bool leader = half == 0 && row == 0;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint8_t* my_p = smem + kOffP + row * 128;
-    uint8_t* my_ds = smem + kOffdS + row * 128;
-    uint8_t* my_stage = smem + kOffStage + row * 128;
-    const int key0 = kt * BKV;
+    uint8_t* my_p = smem + kOffP + half * kTile16 + row * 128;
+    uint8_t* my_ds = smem + kOffdS + half * kTile16 + row * 128;
+    uint8_t* my_stage = smem + kOffStage + half * kTile16 + row * 128;
+    const int key0 = kt * BKV + half * 64;
     bool ok = true;
     constexpr float kLog2e = 1.4426950408889634f;
     for (int n = 0; n < iters; ++n) {
@@ -163,14 +168,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const size_t stat = ((size_t)b * p.H + hq) * p.T + (row_ok ? qi : 0);
       const float L = row_ok ? p.lse[stat] * kLog2e : 0.f;
       const float D = row_ok ? p.delta[stat] : 0.f;
-      if (!mbar_wait(bar_sdp, n & 1, abort_flag)) { ok = false; fail_role = 3; break; }
+      if (!mbar_wait(bar_sdp, n & 1, abort_flag)) ok = false;  // made uniform at the barrier below
       tc_fence_after();
-      const bool need_mask = key0 + BKV - 1 > qt * BQ;
+      const bool need_mask = key0 + 63 > qt * BQ || key0 + 63 >= p.T;
 #pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = 0; c < 2 && ok; ++c) {
         uint32_t rs[32], rp[32];
-        tmem_ld_32x32b_x32(t_lane + kColS + c * 32, rs);
-        tmem_ld_32x32b_x32(t_lane + kColdP + c * 32, rp);
+        tmem_ld_32x32b_x32(t_lane + kColS + half * 64 + c * 32, rs);
+        tmem_ld_32x32b_x32(t_lane + kColdP + half * 64 + c * 32, rp);
         tmem_ld_wait();
         uint32_t pk[16], dk[16];
 #pragma unroll
@@ -179,7 +184,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + c * 32 + i + e;
-            const bool keep = row_ok && key < p.T && (!need_mask || key <= qi);
+            const bool keep = row_ok && (!need_mask || (key <= qi && key < p.T));
             const float prob = keep ? exp2f(__uint_as_float(rs[i + e]) * p.scale_log2 - L) : 0.f;
             pv[e] = prob;
             dv[e] = prob * (__uint_as_float(rp[i + e]) - D) * p.scale;
@@ -188,74 +193,69 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
           dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
         }
-        const int blk = (c >> 1) * kTile16;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          const int chunk = (((c & 1) * 4 + jj) ^ sw) << 4;
-          *reinterpret_cast<uint4*>(my_p + blk + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
-          *reinterpret_cast<uint4*>(my_ds + blk + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
+          const int chunk = ((c * 4 + jj) ^ sw) << 4;
+          *reinterpret_cast<uint4*>(my_p + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+          *reinterpret_cast<uint4*>(my_ds + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar_pds);
-      // dQ partial tile: TMEM -> swizzled fp32 staging (two [128 x 32] boxes) -> TMA reduce-add
-      if (!mbar_wait(bar_dq, n & 1, abort_flag)) { ok = false; fail_role = 3; break; }
+      // dQ partial tile: TMEM -> swizzled fp32 staging (one [128 x 32] box per half) -> TMA reduce-add
+      if (ok && !mbar_wait(bar_dq, n & 1, abort_flag)) ok = false;
       tc_fence_after();
-      if (row == 0) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
-      named_barrier_sync(1, 128);
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      if (leader) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
+      if (named_barrier_or(1, kComputeThreads, !ok)) { ok = false; fail_role = 3; break; }  // all leave together
+      {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + kColdQ + c * 32, r);
+        tmem_ld_32x32b_x32(t_lane + kColdQ + half * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
-          *reinterpret_cast<uint4*>(my_stage + c * kTile16 + ((jj ^ sw) << 4)) = make_uint4(r[4 * jj], r[4 * jj + 1], r[4 * jj + 2], r[4 * jj + 3]);
+          *reinterpret_cast<uint4*>(my_stage + ((jj ^ sw) << 4)) = make_uint4(r[4 * jj], r[4 * jj + 1], r[4 * jj + 2], r[4 * jj + 3]);
       }
       tc_fence_before();
       mbar_arrive(bar_dqr);
       fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
-      if (row == 0) {
+      named_barrier_sync(1, kComputeThreads);
+      if (leader) {
         tma_reduce_add_4d(&tmdQacc, s_base + kOffStage, 0, hq, qt * BQ, b);
         tma_reduce_add_4d(&tmdQacc, s_base + kOffStage + kTile16, 32, hq, qt * BQ, b);
         tma_commit_group();
       }
     }
-    // dK, dV of this key tile: TMEM -> bf16 staging (reuse the P / dS tiles) -> TMA store
+    // dV (half 0) and dK (half 1) of this key tile: TMEM -> bf16 staging (reuse the P / dS tiles) -> TMA store
     if (ok && iters > 0) {
       // bar_dq of the last visit was awaited above, so every MMA (including dV / dK accumulation) has completed
-      if (row == 0) tma_wait_group_read<0>();
-      named_barrier_sync(1, 128);
+      if (leader) tma_wait_group_read<0>();
+      named_barrier_sync(1, kComputeThreads);
+      uint8_t* dst = (half == 0 ? smem + kOffP : smem + kOffdS) + row * 128;
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(t_lane + (half == 0 ? kColdV : kColdK), r0);
+      tmem_ld_32x32b_x32(t_lane + (half == 0 ? kColdV : kColdK) + 32, r1);
+      tmem_ld_wait();
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = (which == 0 ? smem + kOffP : smem + kOffdS) + row * 128;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(t_lane + (which == 0 ? kColdV : kColdK), r0);
-        tmem_ld_32x32b_x32(t_lane + (which == 0 ? kColdV : kColdK) + 32, r1);
-        tmem_ld_wait();
+      for (int jj = 0; jj < 8; ++jj) {
+        uint32_t w[4];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = (jj & 3) * 8 + 2 * e;
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
-            w[e] = *reinterpret_cast<uint32_t*>(&v2);
-          }
-          *reinterpret_cast<uint4*>(dst + ((jj ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int e = 0; e < 4; ++e) {
+          const int i = (jj & 3) * 8 + 2 * e;
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
+          w[e] = *reinterpret_cast<uint32_t*>(&v2);
         }
+        *reinterpret_cast<uint4*>(dst + ((jj ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
-      if (row == 0) {
+      named_barrier_sync(1, kComputeThreads);
+      if (leader) {
         tma_store_4d(&tmdV, s_base + kOffP, 0, kvh, kt * BKV, b);
         tma_store_4d(&tmdK, s_base + kOffdS, 0, kvh, kt * BKV, b);
         tma_commit_group();
       }
     }
-    if (row == 0) tma_wait_group<0>();
+    if (leader) tma_wait_group<0>();
   }
 
   if (fail_role != 0 && p.status != nullptr) {
@@ -273,22 +273,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (b, t, h) row of 64 elements.
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; 8 lanes per (b, t, h) row of 64 elements,
+// 16 bytes per lane per tensor.
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                    float* __restrict__ delta, int B, int T, int H, long long o_sb, long long o_st,
                                    long long o_sh, long long do_sb, long long do_st, long long do_sh) {
-  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long w = gid >> 3;
+  const int sub = threadIdx.x & 7;
   const long long rows = (long long)B * T * H;
-  if (w >= rows) return;
-  const int h = (int)(w % H);
-  const long long bt = w / H;
-  const int t = (int)(bt % T), b = (int)(bt / T);
-  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + b * o_sb + t * o_st + h * o_sh)[lane];
-  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + b * do_sb + t * do_st + h * do_sh)[lane];
-  const float2 af = __bfloat1622float2(a), gf = __bfloat1622float2(g);
-  const float s = warp_sum(af.x * gf.x + af.y * gf.y);
-  if (lane == 0) delta[((size_t)b * H + h) * T + t] = s;
+  float s = 0.f;
+  int h = 0, t = 0, b = 0;
+  if (w < rows) {
+    h = (int)(w % H);
+    const long long bt = w / H;
+    t = (int)(bt % T);
+    b = (int)(bt / T);
+    float a[8], g[8];
+    Chunk8<__nv_bfloat16>::load(o + b * o_sb + t * o_st + h * o_sh + sub * 8, a);
+    Chunk8<__nv_bfloat16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += a[i] * g[i];
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (w < rows && sub == 0) delta[((size_t)b * H + h) * T + t] = s;
 }
 
 // dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous)
@@ -335,7 +345,7 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   if (!nnb_make_tmap_4d(&tdv, dt, 2, dv, hd, KVH, T, B, dv_sh * 2, dv_st * 2, dv_sb * 2, 64, 1, BKV, "flash_bwd dV")) return -4;
 
   const long long rows = (long long)B * T * H;
-  flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+  flash_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
                                                                           (float*)delta, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
   NNB_LAUNCH_OK("flash_delta");
 

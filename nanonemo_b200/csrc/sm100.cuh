@@ -265,6 +265,15 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int fmt_ab, int a_mn, int 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Barrier among `nthreads` threads that also ORs a flag: every participant gets the same answer, so
+// a role whose bounded wait ran out can make all its threads leave together instead of stranding
+// the others at the next barrier.
+__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool flag) {
+  uint32_t out;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 p, %3, 0;\nbarrier.red.or.pred q, %1, %2, p;\nselp.u32 %0, 1, 0, q;\n}"
+               : "=r"(out) : "r"(id), "r"(nthreads), "r"((uint32_t)flag) : "memory");
+  return out != 0;
+}
 
 }  // namespace sm100
 #endif

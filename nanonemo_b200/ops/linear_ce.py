@@ -4,8 +4,9 @@ Row chunks of the flattened hidden states go through: logits chunk (tcgen05 GEMM
 in-place CE kernel (loss per row, logits overwritten with ``(softmax - onehot) / N``) -> ``dx`` chunk
 and ``dW +=`` (tcgen05 GEMMs, the latter accumulating in fp32). As in the reference operator
 (nanonemo/kernels/triton/linear_ce.py:44-80) the gradients are produced during the forward pass and
-backward only rescales them by the upstream gradient; the chunk is sized for B200 (8192 rows: the
-chunk's logits are 0.8 GB instead of the reference's 512-row chunks).
+backward only rescales them by the upstream gradient; the chunk is sized for B200 (32768 rows: one
+chunk's 16-bit logits are 3.3 GB of the 180 GB, and the three GEMMs fill all 148 SMs for several
+waves; the reference uses 512-row chunks on 8 GB parts).
 """
 
 import torch
@@ -13,7 +14,7 @@ import torch
 from nanonemo_b200.ops import _lib
 from nanonemo_b200.ops.gemm import _CODE, compute_dtype, gemm, shadow_of
 
-DEFAULT_CHUNK_ROWS = 8192
+DEFAULT_CHUNK_ROWS = 32768
 
 
 def ce_inplace(logits: torch.Tensor, targets: torch.Tensor, loss_rows: torch.Tensor, grad_scale: float):
@@ -37,7 +38,7 @@ def linear_ce_fwd(x16, w16, targets, chunk_rows, dW_out):
         xc = x16[r0:r1]
         gemm(xc, w16, out=lg)
         ce_inplace(lg, targets[r0:r1], loss_rows[r0:r1], 1.0 / N)
-        gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=128)
+        gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=256 if r1 - r0 >= 16384 else 128)
         gemm(lg, xc, a_mn=True, b_mn=True, out=dW_out, accumulate=True)
     return loss_rows.sum(), dx
 
