@@ -17,6 +17,8 @@
 // 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 compute: two threads per query row,
 // one for keys 0..63 of the tile and one for keys 64..127 (same TMEM lanes, different columns), which
 // halves the latency of the softmax phase the tensor core has to wait for. All waits are bounded.
+#include <type_traits>
+
 #include "sm100.cuh"
 
 namespace {
@@ -160,8 +162,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* my_stage = smem + kOffStage + half * kTile16 + row * 128;
     const int key0 = kt * BKV + half * 64;
     bool ok = true;
+    NNB_PROF_DECL;
     constexpr float kLog2e = 1.4426950408889634f;
     for (int n = 0; n < iters; ++n) {
+      NNB_PROF_T0;
       const int hq = kvh * p.group + n / n_qt, qt = first_qt + n % n_qt;
       const int qi = qt * BQ + row;
       const bool row_ok = qi < p.T;
@@ -170,43 +174,58 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float D = row_ok ? p.delta[stat] : 0.f;
       if (!mbar_wait(bar_sdp, n & 1, abort_flag)) ok = false;  // made uniform at the barrier below
       tc_fence_after();
-      const bool need_mask = key0 + 63 > qt * BQ || key0 + 63 >= p.T;
+      NNB_PROF_ADD(0);
+      // Only tiles on the diagonal, past the end of the sequence, or with padded query rows need the
+      // per-element mask; every other tile takes the branch-free version (5 instructions per element).
+      const bool need_mask = key0 + 63 > qt * BQ || key0 + 63 >= p.T || qt * BQ + BQ > p.T;
+      const float Ds = D * p.scale;
+      auto tile = [&](auto masked) {
+        constexpr bool kMask = decltype(masked)::value;
 #pragma unroll
-      for (int c = 0; c < 2 && ok; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32b_x32(t_lane + kColS + half * 64 + c * 32, rs);
-        tmem_ld_32x32b_x32(t_lane + kColdP + half * 64 + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32b_x32(t_lane + kColS + half * 64 + c * 32, rs);
+          tmem_ld_32x32b_x32(t_lane + kColdP + half * 64 + c * 32, rp);
+          tmem_ld_wait();
+          uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv[2];
+          for (int i = 0; i < 32; i += 2) {
+            float pv[2], dv[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int key = key0 + c * 32 + i + e;
-            const bool keep = row_ok && (!need_mask || (key <= qi && key < p.T));
-            const float prob = keep ? exp2f(__uint_as_float(rs[i + e]) * p.scale_log2 - L) : 0.f;
-            pv[e] = prob;
-            dv[e] = prob * (__uint_as_float(rp[i + e]) - D) * p.scale;
+            for (int e = 0; e < 2; ++e) {
+              float prob = exp2f(__uint_as_float(rs[i + e]) * p.scale_log2 - L);
+              if (kMask) {
+                const int key = key0 + c * 32 + i + e;
+                prob = (row_ok && key <= qi && key < p.T) ? prob : 0.f;
+              }
+              pv[e] = prob;
+              dv[e] = prob * (__uint_as_float(rp[i + e]) * p.scale - Ds);
+            }
+            __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]), d2 = __floats2bfloat162_rn(dv[0], dv[1]);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
+            dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
           }
-          __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]), d2 = __floats2bfloat162_rn(dv[0], dv[1]);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
-          dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
-        }
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int chunk = ((c * 4 + jj) ^ sw) << 4;
-          *reinterpret_cast<uint4*>(my_p + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
-          *reinterpret_cast<uint4*>(my_ds + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
+          for (int jj = 0; jj < 4; ++jj) {
+            const int chunk = ((c * 4 + jj) ^ sw) << 4;
+            *reinterpret_cast<uint4*>(my_p + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+            *reinterpret_cast<uint4*>(my_ds + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
+          }
         }
+      };
+      if (ok) {
+        if (need_mask) tile(std::true_type{});
+        else tile(std::false_type{});
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar_pds);
+      NNB_PROF_ADD(1);
       // dQ partial tile: TMEM -> swizzled fp32 staging (one [128 x 32] box per half) -> TMA reduce-add
       if (ok && !mbar_wait(bar_dq, n & 1, abort_flag)) ok = false;
       tc_fence_after();
       if (leader) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
+      NNB_PROF_ADD(2);
       if (named_barrier_or(1, kComputeThreads, !ok)) { ok = false; fail_role = 3; break; }  // all leave together
       {
         uint32_t r[32];
@@ -225,7 +244,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_reduce_add_4d(&tmdQacc, s_base + kOffStage + kTile16, 32, hq, qt * BQ, b);
         tma_commit_group();
       }
+      NNB_PROF_ADD(3);
     }
+    NNB_PROF_FLUSH_N(iters);
     // dV (half 0) and dK (half 1) of this key tile: TMEM -> bf16 staging (reuse the P / dS tiles) -> TMA store
     if (ok && iters > 0) {
       // bar_dq of the last visit was awaited above, so every MMA (including dV / dK accumulation) has completed
@@ -319,6 +340,10 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
 }
 
 }  // namespace
+
+#ifdef NNB_PROFILE
+extern "C" int nnb_flash_bwd_prof_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_flash_prof, sizeof(g_flash_prof)); }
+#endif
 
 // All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16.
 // lse: fp32 [B, H, T] from the forward pass; delta: fp32 [B, H, T] scratch (written here);

@@ -1,16 +1,17 @@
 // Causal grouped-query FlashAttention forward on tcgen05 / TMEM / TMA for sm_100a.
 //
-// One CTA owns one 128-row query tile of one (batch, query head) and walks the key/value tiles up to
-// the diagonal; TWO such CTAs are resident per SM (112 KB of shared memory and 256 TMEM columns each),
-// so while one CTA's threads do softmax the tensor core works for the other. 320 threads per CTA:
-//   warp 0        TMA producer: Q once, then K_j / V_j into a 2-stage ring (4-D tensor maps over
+// One CTA owns one 128-row query tile of one (batch, query head) and walks the key/value tiles (64 keys
+// each) up to the diagonal; two CTAs are resident per SM at head_dim 64. 192 threads per CTA:
+//   warp 0        TMA producer: Q once, then K_j / V_j into a ring of stages (4-D tensor maps over
 //                 (head_dim, head, t, batch), so any (B,T,H,hd) / (B,H,T,hd) / packed-QKV strides work and
 //                 query head h reads KV head h / group directly — nothing is repeated or copied);
-//   warp 1        MMA issuer: S = Q K_j^T and O_j = P V_j with tcgen05.mma, accumulators in TMEM;
-//   warps 2..9    softmax: two threads per query row (= TMEM lane), one per half of the key columns:
-//                 tcgen05.ld the scores, row max (halves exchanged through shared memory), exp2, bf16 P
-//                 into a 128-byte swizzled shared tile (the A operand of the second MMA), then the
-//                 partial O_j is folded from TMEM into fp32 register accumulators (half of head_dim each).
+//   warp 1        MMA issuer: S_j = Q K_j^T and O_j = P_j V_j with tcgen05.mma, accumulators in TMEM;
+//   warps 2..5    softmax, one thread per query row (= TMEM lane): tcgen05.ld the scores, online max and
+//                 sum with exp2, bf16 P_j into a 128-byte swizzled shared tile (the A operand of the second
+//                 MMA), and the partial O_j folded from TMEM into fp32 register accumulators.
+// The score tile, the P tile and (at head_dim 64) the partial-O tile are DOUBLE BUFFERED and the MMA warp
+// runs two tiles ahead: S_{j+2} is issued as soon as the softmax threads have read S_j, and P_j V_j runs
+// while they work on tile j+1, so neither side waits for a hand-off in steady state.
 // Outputs: O (bf16) through a swizzled staging tile + TMA store, and L = m * scale + ln(l) per row (fp32)
 // for the backward pass. Every mbarrier wait is bounded; on expiry the kernel records a status word
 // and leaves cleanly.
@@ -18,30 +19,36 @@
 // Replaces the reference's WMMA kernel for sm_75 (nanonemo/kernels/cuda/flash_attn.cu:52-174) and
 // the mem-efficient SDPA path it benchmarks against; same math contract (causal, GQA-direct, saves
 // the log-sum-exp per row).
+#include <type_traits>
+
 #include "sm100.cuh"
+
+#ifdef NNB_PROFILE
+extern "C" int nnb_flash_prof_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_flash_prof, sizeof(g_flash_prof)); }
+#endif
 
 namespace {
 
 using namespace sm100;
 
 constexpr int BQ = 128;  // query rows per tile (= TMEM lanes)
-constexpr int kThreads = 320;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 128;
 
 template <int HD>
 struct FCfg {
-  static constexpr int BN = (HD == 64) ? 128 : 64;          // keys per KV tile
-  static constexpr int kStages = 2;
+  static constexpr int BN = 64;                             // keys per KV tile
+  static constexpr int kStages = 3;  // 3 x 16 KB at head_dim 64: two CTAs (2 x ~100 KB) fit in one SM
+  static constexpr int kOBufs = (HD == 64) ? 2 : 1;         // partial-O buffers in TMEM
+  static constexpr int kCtasPerSm = (HD == 64) ? 2 : 1;
   static constexpr int kQBytes = BQ * HD * 2;               // HD/64 swizzled K-blocks of 16 KB
   static constexpr int kKBytes = BN * HD * 2;
   static constexpr int kVBytes = BN * HD * 2;
-  static constexpr int kPBytes = BQ * BN * 2;               // BN/64 swizzled K-blocks of 16 KB
-  static constexpr int kStatBytes = 2 * 2 * BQ * 4;         // row-max exchange, double buffered
-  static constexpr int kSmem = kQBytes + kStages * (kKBytes + kVBytes) + kPBytes + kStatBytes + 1024 + 128;
-  static constexpr int kTmemCols = 256;                     // S at column 0, O at column 128
-  static constexpr int kColS = 0, kColO = 128;
-  static constexpr int kSCols = BN / 2;                     // score columns per softmax thread
-  static constexpr int kOCols = HD / 2;                     // output columns per softmax thread
+  static constexpr int kPBytes = BQ * BN * 2;               // one swizzled K-block of 16 KB per buffer
+  static constexpr int kSmem = kQBytes + kStages * (kKBytes + kVBytes) + 2 * kPBytes + 1024 + 256;
+  static constexpr int kColS = 0;                           // S buffers at columns 0 and 64
+  static constexpr int kColO = 128;                         // partial-O buffers from column 128
+  static constexpr int kTmemCols = (128 + kOBufs * HD) <= 256 ? 256 : 512;
 };
 
 struct FParams {
@@ -55,7 +62,7 @@ struct FParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, FCfg<HD>::kCtasPerSm)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FParams p) {
   using C = FCfg<HD>;
@@ -64,14 +71,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + C::kQBytes;                              // [stages][K | V]
-  uint8_t* sP = sKV + C::kStages * (C::kKBytes + C::kVBytes);
-  float* s_stat = reinterpret_cast<float*>(sP + C::kPBytes);   // [2 parity][2 half][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_stat) + C::kStatBytes);
-  // barriers: q_full, k_full[S], v_full[S], kv_empty[S], s_full, p_full, o_full
+  uint8_t* sP = sKV + C::kStages * (C::kKBytes + C::kVBytes);  // [2][kPBytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::kPBytes);
+  // barriers: q_full, k_full[S], v_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_free[2]
   const uint32_t bar_q = smem_u32(bars);
   const uint32_t bar_k = bar_q + 8, bar_v = bar_k + 8 * C::kStages, bar_e = bar_v + 8 * C::kStages;
-  const uint32_t bar_s = bar_e + 8 * C::kStages, bar_p = bar_s + 8, bar_o = bar_p + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 3 * C::kStages + 3);
+  const uint32_t bar_s = bar_e + 8 * C::kStages, bar_p = bar_s + 16, bar_o = bar_p + 16, bar_of = bar_o + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 3 * C::kStages + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,9 +94,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar_v + 8 * s, 1);
       mbar_init(bar_e + 8 * s, 1);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, kSoftmaxThreads);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s + 8 * i, 1);
+      mbar_init(bar_p + 8 * i, kSoftmaxThreads);
+      mbar_init(bar_o + 8 * i, 1);
+      mbar_init(bar_of + 8 * i, kSoftmaxThreads);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -133,41 +142,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(bar_q, 0, abort_flag);
-      auto issue_s = [&](int j) {
-        const uint32_t sk = smem_u32(sKV) + (j % C::kStages) * (C::kKBytes + C::kVBytes);
+      auto issue_s = [&](int j) -> bool {  // S_j = Q K_j^T into score buffer j & 1
+        const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1;
+        if (!mbar_wait(bar_k + 8 * s, ph, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(sKV) + s * (C::kKBytes + C::kVBytes);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off_q = (k / 4) * (BQ * 128) + (k % 4) * 32, off_k = (k / 4) * (BN * 128) + (k % 4) * 32;
-          umma_f16(tmem_base + C::kColS, make_smem_desc(smem_u32(sQ) + off_q, 16, 1024), make_smem_desc(sk + off_k, 16, 1024),
-                   p.idesc_qk, k > 0 ? 1u : 0u);
+          umma_f16(tmem_base + C::kColS + (j & 1) * BN, make_smem_desc(smem_u32(sQ) + off_q, 16, 1024),
+                   make_smem_desc(sk + off_k, 16, 1024), p.idesc_qk, k > 0 ? 1u : 0u);
         }
-        umma_commit(bar_s);
+        umma_commit(bar_s + 8 * (j & 1));
+        return true;
       };
-      if (ok && n_kv > 0) {
-        ok = mbar_wait(bar_k, 0, abort_flag);
-        if (ok) { tc_fence_after(); issue_s(0); }
-      }
+      if (ok && n_kv > 0) ok = issue_s(0);
+      if (ok && n_kv > 1) ok = issue_s(1);
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1;
+        const int pb = j & 1, ob = j % C::kOBufs;
         if (!mbar_wait(bar_v + 8 * s, ph, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(bar_p, j & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_p + 8 * pb, (j >> 1) & 1, abort_flag)) { ok = false; break; }   // P_j written, S_j consumed
+        if (j >= C::kOBufs && !mbar_wait(bar_of + 8 * ob, ((j / C::kOBufs) - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sv = smem_u32(sKV) + s * (C::kKBytes + C::kVBytes) + C::kKBytes;
+        const uint32_t sp = smem_u32(sP) + pb * C::kPBytes;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint32_t off_p = (k / 4) * (BQ * 128) + (k % 4) * 32;   // P is K-major over keys
-          const uint32_t off_v = k * (16 * 128);                         // V is MN-major: 16 key rows per step
-          umma_f16(tmem_base + C::kColO, make_smem_desc(smem_u32(sP) + off_p, 16, 1024), make_smem_desc(sv + off_v, BN * 128, 1024),
-                   p.idesc_pv, k > 0 ? 1u : 0u);
-        }
-        umma_commit(bar_o);
-        if (j + 1 < n_kv) {
-          const uint32_t s2 = (j + 1) % C::kStages, ph2 = ((j + 1) / C::kStages) & 1;
-          if (!mbar_wait(bar_k + 8 * s2, ph2, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(j + 1);  // the softmax threads finished reading S_j before they arrived on bar_p
-        }
+        for (int k = 0; k < BN / 16; ++k)  // P is K-major over keys; V is MN-major: 16 key rows (2048 B) per step
+          umma_f16(tmem_base + C::kColO + ob * HD, make_smem_desc(sp + k * 32, 16, 1024),
+                   make_smem_desc(sv + k * (16 * 128), BN * 128, 1024), p.idesc_pv, k > 0 ? 1u : 0u);
+        umma_commit(bar_o + 8 * ob);
         umma_commit(bar_e + 8 * s);  // K_j and V_j are free once everything issued so far has run
+        if (j + 2 < n_kv) ok = issue_s(j + 2);  // score buffer j & 1 was released by bar_p above
       }
       if (!ok) fail_role = 2;
     }
@@ -219,7 +225,7 @@ extern "C" int nnb_flash_fwd(const void* q, const void* k, const void* v, void* 
   NNB_REQUIRE(dtype == NNB_BF16, "flash_fwd: bf16 only (dtype code %d)", dtype);
   NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_fwd: bad shape B=%d T=%d H=%d KVH=%d", B, T, H, KVH);
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  const int BN = hd == 64 ? 128 : 64;
+  const int BN = 64;
   CUtensorMap tq, tk, tv, to;
   if (!nnb_make_tmap_4d(&tq, dt, 2, q, hd, H, T, B, q_sh * 2, q_st * 2, q_sb * 2, 64, 1, BQ, "flash Q")) return -4;
   if (!nnb_make_tmap_4d(&tk, dt, 2, k, hd, KVH, T, B, k_sh * 2, k_st * 2, k_sb * 2, 64, 1, BN, "flash K")) return -4;

@@ -104,6 +104,23 @@ static inline bool nnb_make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, in
   return true;
 }
 
+// Optional phase timers (clock64) of one thread of CTA (0,0,0); compiled in only with -DNNB_PROFILE.
+#ifdef NNB_PROFILE
+static __device__ unsigned long long g_flash_prof[8];
+#define NNB_PROF_DECL long long prof_t = 0; unsigned long long prof_acc[5] = {0, 0, 0, 0, 0}
+#define NNB_PROF_T0 prof_t = clock64()
+#define NNB_PROF_ADD(i) do { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define NNB_PROF_FLUSH_N(n_) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64) { \
+  for (int i_ = 0; i_ < 5; ++i_) g_flash_prof[i_] = prof_acc[i_]; g_flash_prof[5] = (n_); } } while (0)
+#define NNB_PROF_FLUSH NNB_PROF_FLUSH_N(n_kv)
+#else
+#define NNB_PROF_DECL
+#define NNB_PROF_T0
+#define NNB_PROF_ADD(i)
+#define NNB_PROF_FLUSH
+#define NNB_PROF_FLUSH_N(n_)
+#endif
+
 #ifdef __CUDACC__
 namespace sm100 {
 
