@@ -1,0 +1,104 @@
+"""Multi-process parity through the real CLI: 2 gloo ranks on CPU must reproduce the single-process
+losses for every layout, resume must equal an uninterrupted run, and a checkpoint written under one
+layout must resume under another (FSDP on 2 ranks -> 1 process; DDP 2 ranks -> TP 2 ranks)."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[2]
+pytestmark = pytest.mark.distributed
+
+CONFIG = """
+model: {n_layers: 2, d_model: 128, n_heads: 4, n_kv_heads: 2, d_ff: 384, vocab_size: 50304, max_seq_len: 128}
+train: {data_dir: synthetic, out_dir: OUT, seq_len: 128, micro_batch: 4, global_batch_tokens: 1024, total_tokens: 6144,
+        peak_lr: 3.0e-4, eval_every: 100, eval_batches: 1, ckpt_async: false}
+"""
+
+
+def run(tmp_path, name, nproc, *overrides, port=29541):
+    out = tmp_path / name
+    cfg = tmp_path / f"{name}.yaml"
+    cfg.write_text(CONFIG.replace("OUT", str(out)))
+    env = dict(os.environ, NANONEMO_DEVICE="cpu", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, str(ROOT / "scripts" / "train.py"), "--config", str(cfg), "--set", *overrides]
+    if nproc > 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port)] + cmd[1:]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    recs = [json.loads(l) for l in (out / "metrics.jsonl").read_text().splitlines()]
+    return [x["loss"] for x in recs if "loss" in x], out
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("single")
+    losses, _ = run(tmp, "single", 1, "train.parallel=none")
+    assert len(losses) == 6
+    return losses
+
+
+@pytest.mark.parametrize("overrides", [
+    ("train.parallel=ddp",),
+    ("train.parallel=ddp", "train.ddp_bucket_mb=0.5", "train.ddp_grad_as_bucket_view=true"),
+    ("train.parallel=fsdp",),
+    ("train.parallel=fsdp", "train.fsdp_prefetch=true", "train.fsdp_reshard_after_forward=false"),
+    ("train.parallel=tp",),
+], ids=["ddp", "ddp_small_buckets", "fsdp", "fsdp_prefetch", "tp"])
+def test_two_ranks_match_one_process(tmp_path, single, overrides):
+    losses, _ = run(tmp_path, "par", 2, *overrides)
+    assert losses == pytest.approx(single, abs=1e-4)
+
+
+def test_grad_accumulation_under_ddp(tmp_path, single):
+    losses, _ = run(tmp_path, "acc", 2, "train.parallel=ddp", "train.micro_batch=2")
+    assert losses == pytest.approx(single, abs=1e-4)
+
+
+@pytest.mark.parametrize("par", ["ddp", "fsdp", "tp"])
+def test_stop_and_resume_matches_uninterrupted(tmp_path, single, par):
+    first, out = run(tmp_path, "r", 2, f"train.parallel={par}", "train.max_steps=3")
+    both, _ = run(tmp_path, "r", 2, f"train.parallel={par}", f"train.resume_from={out / 'ckpt'}")
+    assert len(first) == 3 and both == pytest.approx(single, abs=1e-4)  # the resumed run appends to the same metrics file
+
+
+def test_fsdp_checkpoint_resumes_in_one_process(tmp_path, single):
+    first, out = run(tmp_path, "a", 2, "train.parallel=fsdp", "train.max_steps=3")
+    (tmp_path / "b").mkdir()
+    rest, _ = run(tmp_path, "b", 1, "train.parallel=none", f"train.resume_from={out / 'ckpt'}")
+    assert first + rest == pytest.approx(single, abs=1e-4)
+
+
+def test_ddp_checkpoint_resumes_under_tp(tmp_path, single):
+    first, out = run(tmp_path, "a", 2, "train.parallel=ddp", "train.max_steps=3")
+    rest, _ = run(tmp_path, "b", 2, "train.parallel=tp", f"train.resume_from={out / 'ckpt'}")
+    assert first + rest == pytest.approx(single, abs=1e-4)
+
+
+def test_a_rank_that_never_joins_times_out_on_the_host(tmp_path):
+    """Failure detection without touching a GPU: one of two gloo ranks exits before the rendezvous
+    completes its first collective; the survivor's collective must end with an error within the
+    process-group timeout instead of hanging."""
+    script = tmp_path / "die.py"
+    script.write_text(
+        "import os, sys, torch, torch.distributed as dist\n"
+        f"sys.path.insert(0, {str(ROOT)!r})\n"
+        "from nanonemo_b200 import parallel\n"
+        "d = parallel.init(timeout_s=5)\n"
+        "if d.rank == 1:\n"
+        "    os._exit(0)  # leaves between steps, nothing in flight\n"
+        "try:\n"
+        "    dist.all_reduce(torch.ones(1))\n"
+        "    print('UNEXPECTED: collective completed')\n"
+        "except Exception as e:\n"
+        "    print('PEER LOST:', type(e).__name__)\n"
+        "os._exit(0)\n")
+    env = dict(os.environ, NANONEMO_DEVICE="cpu")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29547", str(script)], env=env, capture_output=True, text=True, timeout=120)
+    assert "PEER LOST" in r.stdout + r.stderr, r.stdout[-1500:] + r.stderr[-1500:]
