@@ -1,0 +1,68 @@
+"""Small profiler target: a few launches of one kernel family at a shape larger than L2 but holding only
+a few hundred MB, so an `ncu --set full` capture ends by itself in about a minute.
+
+    python benchmarks/kernels/ncu_target.py {gemm,flash,rmsnorm,swiglu,rope,ce,adamw} [iters]
+"""
+
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+
+import torch  # noqa: E402
+
+from nanonemo_b200 import ops  # noqa: E402
+
+
+def main():
+    kind = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+    dev, bf = "cuda", torch.bfloat16
+    M = 32768
+    if kind == "gemm":
+        from nanonemo_b200.ops.gemm import gemm
+
+        a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(4096, 768, device=dev, dtype=bf)
+        fn = lambda: gemm(a, b)
+    elif kind == "flash":
+        qkv = torch.randn(8, 1024, 1280, device=dev, dtype=bf, requires_grad=True)
+        fn = lambda: ops.attention_packed(qkv, 12, 4, 64, impl="sm100").sum().backward()
+    elif kind == "rmsnorm":
+        x = torch.randn(M, 768, device=dev, requires_grad=True)
+        d = torch.randn(M, 768, device=dev, dtype=bf, requires_grad=True)
+        w = torch.ones(768, device=dev, requires_grad=True)
+        fn = lambda: sum(t.float().sum() for t in ops.add_rms_norm(x, d, w, 1e-5, impl="sm100")).backward()
+    elif kind == "swiglu":
+        gu = torch.randn(M, 4096, device=dev, dtype=bf, requires_grad=True)
+        fn = lambda: ops.swiglu_packed(gu, impl="sm100").sum().backward()
+    elif kind == "rope":
+        from nanonemo_b200.models.layers import rope_cache
+
+        cos, sin = rope_cache(64, 1024, device=dev)
+        qkv = torch.randn(32, 1024, 1280, device=dev, dtype=bf)
+        fn = lambda: ops.rope_qkv(qkv, cos, sin, 12, 4, 64, impl="sm100")
+    elif kind == "ce":
+        x = torch.randn(4096, 768, device=dev, dtype=bf, requires_grad=True)
+        w = (torch.randn(50304, 768, device=dev) * 0.02).requires_grad_()
+        t = torch.randint(0, 50257, (4096,), device=dev)
+        fn = lambda: ops.linear_cross_entropy(x, w, t).backward()
+    elif kind == "adamw":
+        from nanonemo_b200.ops.adamw import adamw_flat, sumsq
+
+        n = 64 * 1024 * 1024
+        p, g, m, v = (torch.randn(n, device=dev) for _ in range(4))
+        v.abs_()
+        sh = torch.empty(n, device=dev, dtype=bf)
+        fl = torch.ones(n // 256, dtype=torch.uint8, device=dev)
+        fn = lambda: adamw_flat(p, g, m, v, sh, fl, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1,
+                                grad_norm_sq=sumsq(g), max_norm=1.0)
+    else:
+        raise SystemExit(f"unknown target {kind}")
+    for _ in range(iters):
+        fn()
+    torch.cuda.synchronize()
+    print("done", kind)
+
+
+if __name__ == "__main__":
+    main()

@@ -39,8 +39,8 @@ struct Cfg {
   static constexpr int kStageBytesA = BM * BK * 2;
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kTmemCols = 2 * BN;  // 512 or 256: a power of two >= 32
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 4 : 6);
+  static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;  // two accumulators; allocations are powers of two
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -288,20 +288,47 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
   NNB_REQUIRE(dtype == NNB_BF16 || dtype == NNB_F16, "gemm: inputs must be bf16 or fp16 (dtype code %d)", dtype);
   NNB_REQUIRE(!accumulate || out_f32, "gemm: accumulate needs an fp32 output");
   const CUtensorMapDataType in_dt = dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N <= 128 ? 128 : 256);
+  const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
+  const int m_blocks_ = (M + BM - 1) / BM;
+  // Tile width: the widest tile is the most efficient per FLOP, but the number of tiles should fill whole
+  // waves of `sms` persistent CTAs. cost = waves x tile width (a tile's time is proportional to its width).
+  int BN = 256;
+  if (bn_hint == 128 || bn_hint == 192 || bn_hint == 256) {
+    BN = bn_hint;
+  } else if (N <= 128) {
+    BN = 128;
+  } else {
+    double best = 1e30;
+    const int cands[3] = {256, 192, 128};
+    const double eff[3] = {1.0, 1.03, 1.10};  // narrower tiles re-read A more often: small penalty
+    for (int i = 0; i < 3; ++i) {
+      const int bn = cands[i];
+      if (bn == 192 && N % 192 != 0) continue;
+      const long long tiles = (long long)m_blocks_ * ((N + bn - 1) / bn);
+      const double cost = (double)((tiles + sms - 1) / sms) * bn * eff[i];
+      if (cost < best) { best = cost; BN = bn; }
+    }
+    if (out_f32) BN = 256;  // split-K GEMMs balance with the split count instead
+  }
 
   Params p{};
   p.M = M; p.N = N; p.K = K;
   p.m_blocks = (M + BM - 1) / BM;
   p.n_blocks = (N + BN - 1) / BN;
   p.kblocks_total = (K + BK - 1) / BK;
-  const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
   int splits = 1;
   if (out_f32) {
     if (k_splits > 0) splits = k_splits;
     else {
-      const int tiles = p.m_blocks * p.n_blocks;
-      if (tiles < sms) splits = min((2 * sms + tiles - 1) / tiles, max(1, p.kblocks_total / 8));
+      // makespan of `tiles * s` equal items on `sms` persistent CTAs is ceil(tiles * s / sms) / s of the
+      // whole K loop; take the split count that minimises it (ties: fewer splits = less reduce traffic)
+      const long long tiles = (long long)p.m_blocks * p.n_blocks;
+      const int s_max = max(1, min(32, p.kblocks_total / 4));
+      double best = 1e30;
+      for (int sp = 1; sp <= s_max; ++sp) {
+        const double cost = (double)((tiles * sp + sms - 1) / sms) / sp + 0.002 * sp;
+        if (cost < best - 1e-9) { best = cost; splits = sp; }
+      }
     }
     splits = max(1, min(splits, p.kblocks_total));
   }
@@ -329,7 +356,8 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
   }
   const int items = p.m_blocks * p.n_blocks * p.k_splits;
   const int grid = min(items, sms);
-  const int rc = BN == 256 ? launch<256>(tmA, tmB, tmD, p, grid, st) : launch<128>(tmA, tmB, tmD, p, grid, st);
+  const int rc = BN == 256 ? launch<256>(tmA, tmB, tmD, p, grid, st)
+               : BN == 192 ? launch<192>(tmA, tmB, tmD, p, grid, st) : launch<128>(tmA, tmB, tmD, p, grid, st);
   if (rc != 0) return rc;
   NNB_LAUNCH_OK("gemm_tcgen05");
   return 0;

@@ -87,9 +87,18 @@ def build_model(model_cfg: ModelConfig, cfg: TrainConfig, device: str):
 
 
 def build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) -> LocalStrategy:
-    """Lay the model out over the ranks according to cfg.parallel."""
+    """Lay the model out over the ranks according to cfg.parallel (+ the FP8 forward context)."""
     if cfg.precision == "fp8" and not model_cfg.fp8:
         raise ValueError("precision fp8 needs model.linear_impl: mxfp8 (or te)")
+    strategy = _build_parallel(model_cfg, cfg, d)
+    if cfg.precision == "fp8":
+        from nanonemo_b200.fp8 import fp8_context
+
+        strategy.fwd_ctx = fp8_context(cfg.fp8_recipe)
+    return strategy
+
+
+def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) -> LocalStrategy:
     from nanonemo_b200.parallel.flat import FlatParams
 
     if cfg.parallel == "none":

@@ -69,7 +69,7 @@ def test_strided_views_and_bn128():
     big = torch.randn(300, 2048, device=DEV).bfloat16()
     a = big[:, 512:1280]  # row stride 2048, 16-byte aligned offset
     b = torch.randn(768, 768, device=DEV).bfloat16()
-    for bn in (128, 256):
+    for bn in (128, 192, 256):
         out = gemm(a, b, bn=bn)
         check_status()
         _check(out, _ref(a, b, False, False), 768)
