@@ -118,13 +118,24 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TY* __restri
   }
 }
 
-__global__ void dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int rows, int N,
-                                 int accumulate) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= N) return;
+// dw[c] (+)= sum over partial rows; 32 columns per block, 8 threads per column stride over the rows
+// (fixed order within a thread, then a fixed-order combine: the result does not depend on scheduling).
+__global__ void __launch_bounds__(256) dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int rows,
+                                                        int N, int accumulate) {
+  __shared__ float s_red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[(size_t)r * N + i];
-  dw[i] = accumulate ? dw[i] + s : s;
+  if (col < N)
+    for (int r = ry; r < rows; r += 8) s += partial[(size_t)r * N + col];
+  s_red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += s_red[i][cx];
+    dw[col] = accumulate ? dw[col] + t : t;
+  }
 }
 
 // Supported dtype triples (residual TX, delta TD, output TY): the compute dtype C for delta and y,
@@ -206,7 +217,7 @@ extern "C" int nnb_add_rmsnorm_bwd(const void* dy, const void* h, const void* rs
   NNB_REQUIRE(done, "add_rmsnorm_bwd: unsupported dtype combination (x=%d, delta=%d, y=%d)", x_dtype, delta_dtype, y_dtype);
   NNB_REQUIRE(rc == 0, "add_rmsnorm_bwd: cannot raise the shared-memory limit");
   NNB_LAUNCH_OK("add_rmsnorm_bwd");
-  dw_reduce_kernel<<<(N + 255) / 256, 256, 0, st>>>((const float*)dw_partial, (float*)dw, blocks, N, accumulate_dw);
+  dw_reduce_kernel<<<(N + 31) / 32, 256, 0, st>>>((const float*)dw_partial, (float*)dw, blocks, N, accumulate_dw);
   NNB_LAUNCH_OK("rmsnorm_dw_reduce");
   return 0;
 }

@@ -116,12 +116,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
       if (!ok) fail_role = 2;
       const uint32_t sK = s_base + kOffK, sV = s_base + kOffV, sP = s_base + kOffP, sdS = s_base + kOffdS;
-      for (int n = 0; n < iters && ok; ++n) {
+      // S = Q K^T and dP = dO V^T for visit n: all operands K-major, 4 k-steps of 16 over head_dim
+      auto issue_sdp = [&](int n) -> bool {
         const uint32_t s = n % kStagesQ, ph = (n / kStagesQ) & 1;
         const uint32_t sQ = s_base + kOffQdO + s * 2 * kTile16, sdO = sQ + kTile16;
-        if (!mbar_wait(bar_qf + 8 * s, ph, abort_flag)) { ok = false; fail_role = 2; break; }
+        if (!mbar_wait(bar_qf + 8 * s, ph, abort_flag)) return false;
         tc_fence_after();
-        // S = Q K^T and dP = dO V^T: all operands K-major, 4 k-steps of 16 over head_dim
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           umma_f16(tmem_base + kColS, make_smem_desc(sQ + k * 32, 16, 1024), make_smem_desc(sK + k * 32, 16, 1024), p.idesc_s, k > 0);
@@ -129,8 +129,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < HD / 16; ++k)
           umma_f16(tmem_base + kColdP, make_smem_desc(sdO + k * 32, 16, 1024), make_smem_desc(sV + k * 32, 16, 1024), p.idesc_s, k > 0);
         umma_commit(bar_sdp);
-        if (!mbar_wait(bar_pds, n & 1, abort_flag)) { ok = false; fail_role = 2; break; }
-        if (n > 0 && !mbar_wait(bar_dqr, (n - 1) & 1, abort_flag)) { ok = false; fail_role = 2; break; }
+        return true;
+      };
+      if (ok && iters > 0) ok = issue_sdp(0);
+      for (int n = 0; n < iters && ok; ++n) {
+        const uint32_t s = n % kStagesQ;
+        const uint32_t sQ = s_base + kOffQdO + s * 2 * kTile16, sdO = sQ + kTile16;
+        if (!mbar_wait(bar_pds, n & 1, abort_flag)) { ok = false; break; }   // P, dS written; S, dP consumed
+        if (n > 0 && !mbar_wait(bar_dqr, (n - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         // dV += P^T dO and dK += dS^T Q: A = [query][key] tile read MN-major (M = keys: two 64-key groups
         // 16 KB apart), B = [query][hd] tile read MN-major; 8 k-steps of 16 query rows (2048 bytes each).
@@ -149,7 +155,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                    make_smem_desc(sK + k * 2048, kTile16, 1024), p.idesc_dq, k > 0);
         umma_commit(bar_dq);
         umma_commit(bar_qe + 8 * s);
+        // the score tiles of the NEXT visit run on the tensor core while the compute warps drain dQ of this one
+        if (n + 1 < iters) ok = issue_sdp(n + 1);
       }
+      if (!ok) fail_role = 2;
     }
   } else {
     // ------------------------------------------------------------------ compute warps (two threads per query row)

@@ -20,7 +20,9 @@ def test_quantise_matches_reference_rules():
     deq = fp8.dequantize(q, s)
     torch.testing.assert_close(deq, fp8.fake_quant(x).float(), rtol=0, atol=0)
     rel = (deq - x.float()).abs() / amax.repeat_interleave(32, 1)
-    assert rel.max() < 2 ** -4  # e4m3 has 3 mantissa bits: half an ulp of the block maximum's binade
+    # e4m3: 3 mantissa bits (half an ulp of the top binade = 1/16 of the block maximum) and, per the OCP MX rule
+    # scale = 2^(floor(log2 amax) - 8), block maxima that land in (448, 512) saturate to 448 (at most 1/8 off)
+    assert rel.max() < 0.15 and rel.mean() < 0.01
 
 
 def test_fp8_linear_tracks_bf16():
