@@ -74,6 +74,9 @@ def run_ours(a):
                       parallel="ddp" if world > 1 else "none", ddp_bucket_mb=100.0, eval_every=10**9)
     model_cfg, cfg = apply_overrides(model_cfg, cfg, a.set)
 
+    # the clock sampler starts first so that it is already delivering samples when the timed region begins
+    mon = GpuMonitor(100, gpu_index=d.local_rank)
+    mon.__enter__()
     torch.manual_seed(cfg.seed)
     strategy = build_parallel(model_cfg, cfg, d)
     opt = build_optimizer(strategy.model, cfg.peak_lr, cfg.weight_decay, store=strategy.store)
@@ -112,7 +115,7 @@ def run_ours(a):
     for _ in range(a.warmup):
         step(staged, False)
     fence()
-    with GpuMonitor(200, gpu_index=d.local_rank) as mon:
+    try:
         launches0 = _lib.LAUNCHES + strategy.launches
         ms_dev, win_dev, last = timed(staged, False)
         launches = _lib.LAUNCHES + strategy.launches - launches0
@@ -120,10 +123,14 @@ def run_ours(a):
         for _ in range(min(2, a.warmup)):
             step(loader, True)
         ms_e2e, win_e2e, last_e2e = timed(loader, True)
+        time.sleep(0.25)  # let the sampler flush the last lines of the window
+    finally:
+        mon.__exit__(None, None, None)
     tokens = a.steps * cfg.global_batch_tokens
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
-    clocks = clocks_record(mon.window(*win_dev))
+    samples = mon.window(*win_dev) or mon.window(win_dev[0], win_e2e[1])  # a very short device-timed region may fall between two samples
+    clocks = clocks_record(samples)
     flops_tok = flops_per_token(model_cfg, cfg.seq_len)
     if d.main:
         print(json.dumps({

@@ -20,27 +20,12 @@
 // Nothing here waits on a kernel of the same GPU: one rank = one process = one GPU.
 //
 // The reference reaches NCCL through torch DDP / FSDP2 / DTensor (nanonemo/distributed/*.py).
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace {
 
-constexpr int kMaxWorld = 16;
-constexpr uint32_t kPollLimit = 1u << 22;
-constexpr int kCommThreads = 512;
+using namespace nnbcomm;
 
-struct Peers {
-  void* data[kMaxWorld];
-  uint32_t* flags[kMaxWorld];
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
   float4 v;
   asm volatile("ld.global.relaxed.sys.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
@@ -56,38 +41,9 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// Cross-rank barrier among the blocks with this block's index: signal every peer, then wait for
-// every peer. Returns false if a wait ran out (status recorded).
-__device__ bool block_barrier(const Peers& P, int rank, int world, int phase, uint32_t epoch, int* status) {
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __threadfence_system();
-  __syncthreads();
-  const int slot = (phase * gridDim.x + blockIdx.x) * kMaxWorld;
-  if ((int)threadIdx.x < world) {
-    const int peer = threadIdx.x;
-    st_release_sys(P.flags[peer] + slot + rank, epoch);
-    const uint32_t* mine = P.flags[rank] + slot + peer;
-    uint32_t polls = 0;
-    // epochs only grow; signed distance tolerates wrap-around
-    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if (++polls > kPollLimit) {
-        s_fail = 1;
-        if (status != nullptr && atomicCAS(status, 0, 10 + phase) == 0) {
-          status[1] = rank; status[2] = peer; status[3] = blockIdx.x; status[4] = (int)epoch;
-        }
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
-  __syncthreads();
-  return s_fail == 0;
-}
-
 __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, float* mc, int rank, int world, long long lo,
                                                                      long long n, float scale, uint32_t epoch, int* status) {
-  const bool ok = block_barrier(P, rank, world, 0, epoch, status);  // every peer's inputs are final
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);  // every peer's inputs are final
   const long long per = ((n + world - 1) / world + 3) & ~3LL;       // slice length, multiple of 4
   const long long s0 = min((long long)rank * per, n), s1 = min(s0 + per, n);
   const long long n4 = (s1 - s0) >> 2;
@@ -112,7 +68,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, fl
       }
     }
   }
-  block_barrier(P, rank, world, 1, epoch, status);  // every peer's results have landed here
+  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);  // every peer's results have landed here
 }
 
 // out[i] = scale * sum_r data[r][lo + rank*per + i]; sumsq_out += sum(out^2) (one atomic per block).
@@ -120,7 +76,7 @@ __global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers 
                                                                           long long lo, long long per, float scale,
                                                                           uint32_t epoch, int* status) {
   __shared__ float s_part[kCommThreads / 32];
-  const bool ok = block_barrier(P, rank, world, 0, epoch, status);
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);
   const long long n4 = per >> 2;
   float ss = 0.f;
   if (ok) {
@@ -147,14 +103,14 @@ __global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers 
     }
   }
   // peers may overwrite their inputs only after everybody has read them
-  block_barrier(P, rank, world, 1, epoch, status);
+  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);
 }
 
 // local_full[r*per_bytes .. ] = peer r's shard (its bytes [src_off, src_off + per_bytes) ), 16-byte units.
 __global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_t* local_full, int rank, int world,
                                                                  long long src_off, long long per_bytes, uint32_t epoch,
                                                                  int* status) {
-  const bool ok = block_barrier(P, rank, world, 0, epoch, status);  // every peer's shard is final
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);  // every peer's shard is final
   const long long n16 = per_bytes >> 4;
   if (ok) {
     for (int rr = 0; rr < world; ++rr) {
@@ -168,19 +124,7 @@ __global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_
       }
     }
   }
-  block_barrier(P, rank, world, 1, epoch, status);  // shards may be rewritten once everybody has copied them
-}
-
-int fill_peers(Peers& P, void* const* data_ptrs, void* const* flag_ptrs, int world) {
-  if (world < 1 || world > kMaxWorld) {
-    nnb_set_error("comm: world size %d not supported (1..%d)", world, kMaxWorld);
-    return -1;
-  }
-  for (int r = 0; r < kMaxWorld; ++r) {
-    P.data[r] = r < world ? data_ptrs[r] : nullptr;
-    P.flags[r] = r < world ? static_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
-  }
-  return 0;
+  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);  // shards may be rewritten once everybody has copied them
 }
 
 }  // namespace

@@ -22,6 +22,7 @@
 //
 // This replaces the cuBLAS calls behind nn.Linear in the reference (nanonemo/model/layers.py:80-83,
 // 128-130); the reference ships no tensor-core GEMM of its own.
+#include "comm.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -52,12 +53,28 @@ struct Params {
   int reduce_add;       // epilogue uses TMA reduce-add (fp32 only)
   uint32_t idesc;
   int* status;          // device int[4]: {code, role, block, item}; code 0 = ok
+  // ---- fused collectives (mode 0: none)
+  //  mode 1  GEMM -> reduce-scatter: output rows are sharded over `world` ranks (mblocks_per_rank m-blocks each);
+  //          every tile is TMA-reduce-added straight into the OWNER rank's buffer over NVLink (tmDs.m[owner]).
+  //  mode 2  all-gather -> GEMM: A rows are sharded over the ranks in a symmetric buffer; the first `gather_ctas`
+  //          CTAs pull the peers' shards into the local buffer m-block by m-block and publish a ready flag per
+  //          m-block; the other CTAs start on the local rows and wait (bounded) for a flag before a remote block.
+  int mode, world, rank, mblocks_per_rank, gather_ctas;
+  uint32_t epoch;
+  uint32_t* local_flags;  // device uint32: [0] go flag, [1] finished-CTA counter, [2 + m_blk] m-block ready flags
+  long long a_row_bytes;  // mode 2: bytes of one row of A (rows are contiguous)
+  int* comm_status;       // device int[8] for the collective part
+  nnbcomm::Peers peers;   // flags of every rank; data = every rank's A buffer (mode 2)
+};
+
+struct DMaps {
+  CUtensorMap m[8];       // mode 1: one output map per rank; otherwise m[0]
 };
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmD, const Params p) {
+                    const __grid_constant__ DMaps tmDs, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,7 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    tma_prefetch_desc(&tmD);
+    tma_prefetch_desc(&tmDs.m[0]);
   }
   tc_fence_before();
   __syncthreads();
@@ -102,16 +119,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int items = p.m_blocks * p.n_blocks * p.k_splits;
   int fail_role = 0, fail_item = -1;
+  // compute CTAs: index cta0 of nctas (in mode 2 the first gather_ctas CTAs only move data)
+  const int first_compute = p.mode == 2 ? p.gather_ctas : 0;
+  const int cta0 = (int)blockIdx.x - first_compute, nctas = (int)gridDim.x - first_compute;
+  // m-block visited at position `ord`: mode 2 starts with this rank's own rows, then follows the gather order
+  auto m_of = [&](int ord) { return p.mode == 2 ? (p.rank * p.mblocks_per_rank + ord) % p.m_blocks : ord; };
 
-  if (warp == 0) {
+  if (p.mode == 1 && blockIdx.x == 0) {
+    // every rank's output buffer has been zeroed (stream order on each rank) before anybody adds into it
+    const bool ok = nnbcomm::block_barrier(p.peers, p.rank, p.world, 0, 0, 1, p.epoch, p.comm_status);
+    if (threadIdx.x == 0) nnbcomm::st_release_gpu(p.local_flags, ok ? p.epoch : p.epoch - 1);
+  }
+
+  if (p.mode == 2 && cta0 < 0) {
+    // ------------------------------------------------------------------ gather CTAs (all threads copy)
+    const int G = p.gather_ctas, me = blockIdx.x;
+    bool ok = nnbcomm::block_barrier(p.peers, p.rank, p.world, 0, me, G, p.epoch, p.comm_status);  // peers' shards are final
+    const long long mb_bytes = (long long)BM * p.a_row_bytes;
+    const int nvec = (int)(mb_bytes >> 4);
+    for (int step = 1; step < p.world && ok; ++step) {
+      const int r = (p.rank + step) % p.world;
+      for (int mb = me; mb < p.mblocks_per_rank; mb += G) {
+        const long long off = (long long)(r * p.mblocks_per_rank + mb) * mb_bytes;
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.peers.data[r]) + off);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peers.data[p.rank]) + off);
+        for (int i = threadIdx.x; i < nvec; i += kThreads * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + u * kThreads < nvec)
+              asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + u * kThreads) : "memory");
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + u * kThreads < nvec) dst[i + u * kThreads] = v[u];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) nnbcomm::st_release_gpu(p.local_flags + 2 + r * p.mblocks_per_rank + mb, p.epoch);
+      }
+    }
+    // my shard may be overwritten only after every peer has copied it
+    nnbcomm::block_barrier(p.peers, p.rank, p.world, 1, me, G, p.epoch, p.comm_status);
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      for (int item = cta0; item < items && ok; item += nctas) {
         const int ks = item % p.k_splits, tile = item / p.k_splits;
-        const int n_blk = tile % p.n_blocks, m_blk = tile / p.n_blocks;
+        const int n_blk = tile % p.n_blocks, m_blk = m_of(tile / p.n_blocks);
         const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        if (p.mode == 2 && m_blk / p.mblocks_per_rank != p.rank) {
+          // rows of a peer: wait until a gather CTA has landed this m-block in the local buffer
+          const uint32_t* flag = p.local_flags + 2 + m_blk;
+          uint32_t polls = 0;
+          while ((int32_t)(nnbcomm::ld_acquire_gpu(flag) - p.epoch) < 0) {
+            if (++polls > nnbcomm::kPollLimit || *abort_flag) { ok = false; *abort_flag = 1; fail_role = 4; fail_item = item; break; }
+            __nanosleep(32);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of the gather CTAs -> TMA reads
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; fail_role = 1; fail_item = item; break; }
@@ -147,7 +216,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t a_step = p.a_mn ? (16 * 128) >> 4 : 32 >> 4;  // descriptor start-address step per UMMA_K = 16
       const uint32_t b_step = p.b_mn ? (16 * 128) >> 4 : 32 >> 4;
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++tile_iter) {
+      for (int item = cta0; item < items && ok; item += nctas, ++tile_iter) {
         const int ks = item % p.k_splits;
         const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         const uint32_t acc = tile_iter & 1, acc_ph = (tile_iter >> 1) & 1;
@@ -175,9 +244,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int et = threadIdx.x - 64;        // 0..127
     uint32_t tile_iter = 0, gchunk = 0;  // gchunk: staging buffers alternate across tiles too
     int pending_stores = 0;
-    for (int item = blockIdx.x; item < items; item += gridDim.x, ++tile_iter) {
+    bool go = p.mode != 1;  // mode 1: the first reduce waits until every rank has zeroed its output
+    for (int item = cta0; item < items; item += nctas, ++tile_iter) {
       const int tile = item / p.k_splits;
-      const int n_blk = tile % p.n_blocks, m_blk = tile / p.n_blocks;
+      const int n_blk = tile % p.n_blocks, m_blk = m_of(tile / p.n_blocks);
+      // where the tile goes: mode 1 = the owner rank's buffer (peer memory), row offset inside its shard
+      const int owner = p.mode == 1 ? m_blk / p.mblocks_per_rank : 0;
+      const int d_row = p.mode == 1 ? (m_blk - owner * p.mblocks_per_rank) * BM : m_blk * BM;
+      const CUtensorMap* tmD = &tmDs.m[owner];
       const uint32_t acc = tile_iter & 1, acc_ph = (tile_iter >> 1) & 1;
       const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag);
       if (!ok) { fail_role = 3; fail_item = item; }
@@ -194,6 +268,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
         ++gchunk;
         if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();  // the store that last read `buf` is done
+        if (!go) {
+          if (et == 0) {
+            uint32_t polls = 0;
+            while ((int32_t)(nnbcomm::ld_acquire_gpu(p.local_flags) - p.epoch) < 0 && ++polls < nnbcomm::kPollLimit) __nanosleep(64);
+            if (polls >= nnbcomm::kPollLimit) *abort_flag = 1;
+          }
+          go = true;
+        }
         named_barrier_sync(1, kEpilogueThreads);
         uint8_t* my_row = buf + row * 128;
         const int sw = row & 7;
@@ -231,8 +313,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_proxy_async_smem();
         named_barrier_sync(1, kEpilogueThreads);
         if (et == 0) {
-          if (p.reduce_add) tma_reduce_add_2d(&tmD, smem_u32(buf), n_blk * BN + col0, m_blk * BM);
-          else tma_store_2d(&tmD, smem_u32(buf), n_blk * BN + col0, m_blk * BM);
+          if (p.reduce_add) tma_reduce_add_2d(tmD, smem_u32(buf), n_blk * BN + col0, d_row);
+          else tma_store_2d(tmD, smem_u32(buf), n_blk * BN + col0, d_row);
           tma_commit_group();
         }
         if (pending_stores < 2) ++pending_stores;
@@ -258,10 +340,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if (p.mode == 1) {
+    // The last CTA of this rank to finish meets the last CTAs of the peers: when the kernel ends on a rank,
+    // every rank's contributions to its shard have landed.
+    __shared__ int s_last;
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      s_last = atomicAdd(p.local_flags + 1, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+      nnbcomm::block_barrier(p.peers, p.rank, p.world, 1, 0, 1, p.epoch, p.comm_status);
+      if (threadIdx.x == 0) p.local_flags[1] = 0u;
+    }
+  }
 }
 
 template <int BN>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const Params& p, int grid, cudaStream_t st) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const DMaps& tmDs, const Params& p, int grid, cudaStream_t st) {
   auto kern = gemm_tcgen05_kernel<BN>;
   static bool configured = false;
   if (!configured) {
@@ -271,22 +367,30 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
     }
     configured = true;
   }
-  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, st>>>(tmA, tmB, tmD, p);
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, st>>>(tmA, tmB, tmDs, p);
   return 0;
 }
 
 }  // namespace
 
-// A, B: 16-bit (dtype: 1 = bf16, 2 = fp16). lda/ldb/ldd: row strides in ELEMENTS of the stored matrices:
-//   A K-major stored [M, K] (lda >= K); A MN-major stored [K, M] (lda >= M); same for B with N.
-// D stored [M, N] row-major with ldd; out_f32 selects fp32 output, accumulate adds into D (fp32 only).
-// k_splits <= 0 picks a split automatically (only used with fp32 output). status: device int[4] or null.
-extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
-                             long long ldd, int a_mn, int b_mn, int dtype, int out_f32, int accumulate, int k_splits,
-                             int bn_hint, int max_ctas, void* status, cudaStream_t st) {
+namespace {
+
+struct CommArgs {           // mode 0 when null
+  int mode, world, rank, gather_ctas;
+  void* const* data_ptrs;   // mode 1: every rank's output shard buffer; mode 2: every rank's full A buffer
+  void* const* flag_ptrs;   // symmetric uint32 flag buffers (nnb_comm_flag_words(max(1, gather_ctas)))
+  void* local_flags;        // device uint32 [2 + m_blocks], zero before the first call
+  void* comm_status;        // device int[8]
+  int epoch;
+};
+
+int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn,
+              int b_mn, int dtype, int out_f32, int accumulate, int k_splits, int bn_hint, int max_ctas, void* status,
+              const CommArgs* comm, cudaStream_t st) {
   NNB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %dx%dx%d", M, N, K);
   NNB_REQUIRE(dtype == NNB_BF16 || dtype == NNB_F16, "gemm: inputs must be bf16 or fp16 (dtype code %d)", dtype);
-  NNB_REQUIRE(!accumulate || out_f32, "gemm: accumulate needs an fp32 output");
+  const int mode = comm ? comm->mode : 0;
+  NNB_REQUIRE(!accumulate || out_f32 || mode == 1, "gemm: accumulate needs an fp32 output");
   const CUtensorMapDataType in_dt = dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
   const int m_blocks_ = (M + BM - 1) / BM;
@@ -299,11 +403,10 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
     BN = 128;
   } else {
     double best = 1e30;
-    const int cands[3] = {256, 192, 128};
-    const double eff[3] = {1.0, 1.03, 1.10};  // narrower tiles re-read A more often: small penalty
-    for (int i = 0; i < 3; ++i) {
+    const int cands[2] = {256, 128};  // 192-wide tiles measured slower even where they fill the waves better (kept behind bn_hint)
+    const double eff[2] = {1.0, 1.10};  // narrower tiles re-read A more often: small penalty
+    for (int i = 0; i < 2; ++i) {
       const int bn = cands[i];
-      if (bn == 192) continue;  // measured slower than 256-wide tiles even where it fills the waves better; kept behind bn_hint
       const long long tiles = (long long)m_blocks_ * ((N + bn - 1) / bn);
       const double cost = (double)((tiles + sms - 1) / sms) * bn * eff[i];
       if (cost < best) { best = cost; BN = bn; }
@@ -317,7 +420,7 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
   p.n_blocks = (N + BN - 1) / BN;
   p.kblocks_total = (K + BK - 1) / BK;
   int splits = 1;
-  if (out_f32) {
+  if (out_f32 && mode == 0) {
     if (k_splits > 0) splits = k_splits;
     else {
       // makespan of `tiles * s` equal items on `sms` persistent CTAs is ceil(tiles * s / sms) / s of the
@@ -337,17 +440,44 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
   p.a_mn = a_mn ? 1 : 0;
   p.b_mn = b_mn ? 1 : 0;
   p.out_f32 = out_f32 ? 1 : 0;
-  p.reduce_add = (accumulate || p.k_splits > 1) ? 1 : 0;
+  p.reduce_add = (accumulate || p.k_splits > 1 || mode == 1) ? 1 : 0;
   p.idesc = sm100::make_idesc_f16(dtype == NNB_BF16 ? 1 : 0, p.a_mn, p.b_mn, BM, BN);
   p.status = static_cast<int*>(status);
+  p.mode = mode;
 
-  CUtensorMap tmA, tmB, tmD;
+  CUtensorMap tmA, tmB;
+  DMaps tmDs;
   if (!p.a_mn) { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, A, M, K, lda * 2, BM, BK, "gemm A")) return -4; }
   else         { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, A, K, M, lda * 2, BK, 64, "gemm A^T")) return -4; }
   if (!p.b_mn) { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, B, N, K, ldb * 2, BN, BK, "gemm B")) return -4; }
   else         { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, B, K, N, ldb * 2, BK, 64, "gemm B^T")) return -4; }
-  if (out_f32) { if (!nnb_make_tmap_2d(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, D, M, N, ldd * 4, BM, 32, "gemm D")) return -4; }
-  else         { if (!nnb_make_tmap_2d(&tmD, in_dt, 2, D, M, N, ldd * 2, BM, 64, "gemm D")) return -4; }
+  const CUtensorMapDataType d_dt = out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : in_dt;
+  const int d_bytes = out_f32 ? 4 : 2, d_box = out_f32 ? 32 : 64;
+  if (mode == 1) {
+    NNB_REQUIRE(comm->world >= 1 && comm->world <= 8, "gemm_rs: world %d not supported (1..8)", comm->world);
+    NNB_REQUIRE(!a_mn && M % (BM * comm->world) == 0, "gemm_rs: M=%d must be a multiple of %d x world", M, BM);
+    const int rows = M / comm->world;
+    for (int r = 0; r < comm->world; ++r)
+      if (!nnb_make_tmap_2d(&tmDs.m[r], d_dt, d_bytes, comm->data_ptrs[r], rows, N, ldd * d_bytes, BM, d_box, "gemm_rs D")) return -4;
+    for (int r = comm->world; r < 8; ++r) tmDs.m[r] = tmDs.m[0];
+  } else {
+    if (!nnb_make_tmap_2d(&tmDs.m[0], d_dt, d_bytes, D, M, N, ldd * d_bytes, BM, d_box, "gemm D")) return -4;
+    for (int r = 1; r < 8; ++r) tmDs.m[r] = tmDs.m[0];
+  }
+  if (mode != 0) {
+    p.world = comm->world; p.rank = comm->rank;
+    p.mblocks_per_rank = p.m_blocks / comm->world;
+    p.gather_ctas = mode == 2 ? comm->gather_ctas : 0;
+    p.epoch = (uint32_t)comm->epoch;
+    p.local_flags = static_cast<uint32_t*>(comm->local_flags);
+    p.comm_status = static_cast<int*>(comm->comm_status);
+    p.a_row_bytes = lda * 2;
+    if (nnbcomm::fill_peers(p.peers, mode == 2 ? comm->data_ptrs : nullptr, comm->flag_ptrs, comm->world) != 0) return -1;
+    if (mode == 2) {
+      NNB_REQUIRE(!a_mn && lda == K && M % (BM * comm->world) == 0, "ag_gemm: A must be contiguous [M, K] with M a multiple of %d x world", BM);
+      NNB_REQUIRE(comm->gather_ctas >= 1 && comm->gather_ctas < sms, "ag_gemm: bad gather CTA count %d", comm->gather_ctas);
+    }
+  }
 
   if (out_f32 && !accumulate && p.k_splits > 1) {
     // partial tiles are reduce-added: start from zero
@@ -355,10 +485,49 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
     else cudaMemset2DAsync(D, ldd * 4, 0, (size_t)N * 4, M, st);
   }
   const int items = p.m_blocks * p.n_blocks * p.k_splits;
-  const int grid = min(items, sms);
-  const int rc = BN == 256 ? launch<256>(tmA, tmB, tmD, p, grid, st)
-               : BN == 192 ? launch<192>(tmA, tmB, tmD, p, grid, st) : launch<128>(tmA, tmB, tmD, p, grid, st);
+  int grid = min(items, sms);
+  if (mode == 2) grid = min(items + p.gather_ctas, sms);
+  const int rc = BN == 256 ? launch<256>(tmA, tmB, tmDs, p, grid, st)
+               : BN == 192 ? launch<192>(tmA, tmB, tmDs, p, grid, st) : launch<128>(tmA, tmB, tmDs, p, grid, st);
   if (rc != 0) return rc;
   NNB_LAUNCH_OK("gemm_tcgen05");
   return 0;
+}
+
+}  // namespace
+
+// A, B: 16-bit (dtype: 1 = bf16, 2 = fp16). lda/ldb/ldd: row strides in ELEMENTS of the stored matrices:
+//   A K-major stored [M, K] (lda >= K); A MN-major stored [K, M] (lda >= M); same for B with N.
+// D stored [M, N] row-major with ldd; out_f32 selects fp32 output, accumulate adds into D (fp32 only).
+// k_splits <= 0 picks a split automatically (only used with fp32 output). status: device int[4] or null.
+extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                             long long ldd, int a_mn, int b_mn, int dtype, int out_f32, int accumulate, int k_splits,
+                             int bn_hint, int max_ctas, void* status, cudaStream_t st) {
+  return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, dtype, out_f32, accumulate, k_splits, bn_hint, max_ctas, status,
+                   nullptr, st);
+}
+
+// GEMM -> reduce-scatter in one kernel (row-parallel linear under tensor + sequence parallelism):
+//   out_shard[rank r] [M / world, N]  +=  (A[M, K] @ B[N, K]^T) rows [r M / world, (r + 1) M / world)   summed over ranks.
+// Every output tile is TMA-reduce-added into the owner's buffer over NVLink as soon as it leaves TMEM, so the
+// transfer overlaps the math tile by tile. out_ptrs: every rank's shard buffer (symmetric memory), ZEROED by its
+// owner earlier on this stream; the kernel itself waits until every rank has done so and, before it ends, until
+// every rank has finished adding. local_flags: device uint32[>= 2], zero before the first call.
+extern "C" int nnb_gemm_rs_bf16(const void* A, const void* B, void* const* out_ptrs, void* const* flag_ptrs, void* local_flags,
+                                void* comm_status, int rank, int world, int epoch, int M, int N, int K, long long lda,
+                                long long ldb, long long ldd, int b_mn, int dtype, int out_f32, void* status, cudaStream_t st) {
+  CommArgs c{1, world, rank, 0, out_ptrs, flag_ptrs, local_flags, comm_status, epoch};
+  return gemm_impl(A, B, nullptr, M, N, K, lda, ldb, ldd, 0, b_mn, dtype, out_f32, 1, 1, 0, 0, status, &c, st);
+}
+
+// all-gather -> GEMM in one kernel (column-parallel linear under tensor + sequence parallelism):
+//   D[M, N] = A_full[M, K] @ B[N, K]^T where rank r owns rows [r M / world, (r + 1) M / world) of A_full.
+// a_ptrs: every rank's full-size A buffer (symmetric memory) holding valid data in ITS OWN row range; the first
+// gather_ctas CTAs copy the peers' ranges into this rank's buffer m-block by m-block while the other CTAs
+// multiply, starting with the local rows. local_flags: device uint32[2 + M / 128], zero before the first call.
+extern "C" int nnb_ag_gemm_bf16(void* const* a_ptrs, const void* B, void* D, void* const* flag_ptrs, void* local_flags,
+                                void* comm_status, int rank, int world, int epoch, int gather_ctas, int M, int N, int K,
+                                long long ldb, long long ldd, int b_mn, int dtype, void* status, cudaStream_t st) {
+  CommArgs c{2, world, rank, gather_ctas, a_ptrs, flag_ptrs, local_flags, comm_status, epoch};
+  return gemm_impl(a_ptrs[rank], B, D, M, N, K, K, ldb, ldd, 0, b_mn, dtype, 0, 0, 1, 0, 0, status, &c, st);
 }

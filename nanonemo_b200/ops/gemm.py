@@ -130,3 +130,65 @@ class _Linear(torch.autograd.Function):
 
 def linear_sm100(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return _Linear.apply(x, weight)
+
+
+# ----------------------------------------------------------------------------- GEMMs fused with a collective
+class FusedCollectiveGemm:
+    """Per-group state for the two single-kernel compute+collective GEMMs (csrc/gemm.cu modes 1 and 2):
+    the symmetric flag buffer, the local flag words, the epoch counter and the status words.
+
+    ``gemm_rs(a, b, out)``  row-parallel linear: every rank multiplies its K-slice for ALL rows and each
+    output tile is TMA-reduce-added over NVLink into the rank that owns those rows (``out`` is a
+    ``SymmetricBuffer`` holding this rank's [M / world, N] shard).
+    ``ag_gemm(a_full, b)``  column-parallel linear: ``a_full`` is a ``SymmetricBuffer`` of the FULL
+    [M, K] activation in which each rank has written only its own row range; a few CTAs pull the peers'
+    ranges in while the rest multiply, starting with the local rows.
+    """
+
+    def __init__(self, device, group, rank: int, world: int, max_m_blocks: int = 4096, gather_ctas: int = 16):
+        from nanonemo_b200.parallel.symm import SymmetricBuffer
+
+        self.rank, self.world, self.group, self.gather_ctas = rank, world, group, gather_ctas
+        words = _lib.lib().nnb_comm_flag_words(max(1, gather_ctas))
+        self.flags = SymmetricBuffer(words, torch.int32, device, group)
+        self.flags.tensor.zero_()
+        self.local_flags = torch.zeros(2 + max_m_blocks, dtype=torch.int32, device=device)
+        self.comm_status = torch.zeros(8, dtype=torch.int32, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        torch.distributed.barrier(group)
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, out, *, b_mn: bool = False, out_f32: bool = False):
+        """a: [M, K_local]; b: [N, K_local] (or [K_local, N] when b_mn); out: SymmetricBuffer viewed as
+        [M / world, N]. Returns this rank's reduced shard (valid once the kernel has run)."""
+        a, b = _rowmajor2d(a), _rowmajor2d(b)
+        M, K = a.shape
+        N = b.shape[1] if b_mn else b.shape[0]
+        shard = out.tensor.view(-1)[: (M // self.world) * N].view(M // self.world, N)
+        shard.zero_()
+        self.epoch += 1
+        _lib.call("nnb_gemm_rs_bf16", _lib.ptr(a), _lib.ptr(b), out.ptr_array, self.flags.ptr_array, _lib.ptr(self.local_flags),
+                  _lib.ptr(self.comm_status), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.epoch), _lib.i32(M),
+                  _lib.i32(N), _lib.i32(K), _lib.i64(a.stride(0)), _lib.i64(b.stride(0)), _lib.i64(N), _lib.i32(int(b_mn)),
+                  _lib.i32(_CODE[a.dtype]), _lib.i32(int(out_f32)), _lib.ptr(status_tensor(a.device)), _lib.vp(_lib.stream_ptr()))
+        return shard
+
+    def ag_gemm(self, a_full, M: int, K: int, b: torch.Tensor, *, b_mn: bool = False, out: torch.Tensor | None = None):
+        """a_full: SymmetricBuffer holding [M, K] 16-bit with this rank's rows already written."""
+        b = _rowmajor2d(b)
+        N = b.shape[1] if b_mn else b.shape[0]
+        dtype = a_full.tensor.dtype
+        out = out if out is not None else torch.empty((M, N), dtype=dtype, device=b.device)
+        self.epoch += 1
+        _lib.call("nnb_ag_gemm_bf16", a_full.ptr_array, _lib.ptr(b), _lib.ptr(out), self.flags.ptr_array, _lib.ptr(self.local_flags),
+                  _lib.ptr(self.comm_status), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.epoch),
+                  _lib.i32(self.gather_ctas), _lib.i32(M), _lib.i32(N), _lib.i32(K), _lib.i64(b.stride(0)), _lib.i64(out.stride(0)),
+                  _lib.i32(int(b_mn)), _lib.i32(_CODE[dtype]), _lib.ptr(status_tensor(b.device)), _lib.vp(_lib.stream_ptr()))
+        return out
+
+    def check_status(self):
+        st = self.comm_status.tolist()
+        if st[0] != 0:
+            self.comm_status.zero_()
+            raise RuntimeError(f"fused GEMM collective gave up waiting: code={st[0]} rank={st[1]} peer={st[2]} block={st[3]} epoch={st[4]}")
+        check_status()
