@@ -135,30 +135,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------------ gather CTAs (all threads copy)
     const int G = p.gather_ctas, me = blockIdx.x;
     bool ok = nnbcomm::block_barrier(p.peers, p.rank, p.world, 0, me, G, p.epoch, p.comm_status);  // peers' shards are final
-    const long long mb_bytes = (long long)BM * p.a_row_bytes;
-    const int nvec = (int)(mb_bytes >> 4);
-    for (int step = 1; step < p.world && ok; ++step) {
-      const int r = (p.rank + step) % p.world;
-      for (int mb = me; mb < p.mblocks_per_rank; mb += G) {
-        const long long off = (long long)(r * p.mblocks_per_rank + mb) * mb_bytes;
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.peers.data[r]) + off);
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peers.data[p.rank]) + off);
-        for (int i = threadIdx.x; i < nvec; i += kThreads * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (i + u * kThreads < nvec)
-              asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + u * kThreads) : "memory");
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (i + u * kThreads < nvec) dst[i + u * kThreads] = v[u];
+    // One thread drives bulk asynchronous copies through the (otherwise unused) operand stages of this CTA:
+    // peer memory -> shared memory (cp.async.bulk, completion on an mbarrier) -> local memory (bulk store), so a
+    // handful of CTAs keep megabytes in flight over NVLink. An m-block's ready flag is published once its last
+    // store group has completed.
+    if (threadIdx.x == 0 && ok) {
+      const long long mb_bytes = (long long)BM * p.a_row_bytes;
+      int chunk_rows = BM;
+      while (chunk_rows > 1 && (long long)chunk_rows * p.a_row_bytes > C::kStageBytes) chunk_rows >>= 1;
+      const uint32_t chunk_bytes = (uint32_t)(chunk_rows * p.a_row_bytes);
+      const int chunks_per_mb = BM / chunk_rows;
+      const int my_mbs = (p.mblocks_per_rank - me + G - 1) / G;            // m-blocks of each peer handled here
+      const int total = (p.world - 1) * my_mbs * chunks_per_mb;           // chunks to move
+      constexpr int S = C::kStages;
+      constexpr int kLag = 2;                                             // stores trail the loads by S - kLag chunks
+      auto locate = [&](int i, long long& off, int& flag_idx, bool& last) {
+        const int c = i % chunks_per_mb, mbi = (i / chunks_per_mb) % my_mbs, step = 1 + i / (chunks_per_mb * my_mbs);
+        const int r = (p.rank + step) % p.world, mb = me + mbi * G;
+        off = (long long)(r * p.mblocks_per_rank + mb) * mb_bytes + (long long)c * chunk_bytes;
+        flag_idx = r * p.mblocks_per_rank + mb;
+        last = c == chunks_per_mb - 1;
+        return r;
+      };
+      auto store_chunk = [&](int j) -> bool {
+        long long off; int fi; bool last;
+        locate(j, off, fi, last);
+        const uint32_t s = j % S;
+        if (!mbar_wait(bar_full + 8 * s, (j / S) & 1, abort_flag)) return false;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(static_cast<uint8_t*>(p.peers.data[p.rank]) + off),
+                     "r"(smem_u32(stage_base + s * C::kStageBytes)), "r"(chunk_bytes) : "memory");
+        tma_commit_group();
+        return true;
+      };
+      auto publish_if_last = [&](int j) {
+        long long off; int fi; bool last;
+        locate(j, off, fi, last);
+        if (last) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          nnbcomm::st_release_gpu(p.local_flags + 2 + fi, p.epoch);
         }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) nnbcomm::st_release_gpu(p.local_flags + 2 + r * p.mblocks_per_rank + mb, p.epoch);
+      };
+      for (int i = 0; i < total + (S - kLag) && ok; ++i) {
+        if (i < total) {
+          long long off; int fi; bool last;
+          const int r = locate(i, off, fi, last);
+          const uint32_t s = i % S;
+          mbar_expect_tx(bar_full + 8 * s, chunk_bytes);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(stage_base + s * C::kStageBytes)), "l"(static_cast<const uint8_t*>(p.peers.data[r]) + off),
+                         "r"(chunk_bytes), "r"(bar_full + 8 * s) : "memory");
+        }
+        const int j = i - (S - kLag);
+        if (j >= 0 && j < total) {
+          if (!store_chunk(j)) { ok = false; break; }
+          // at most kLag - 1 store groups stay pending: the stage the next load overwrites has been read, and
+          // everything older is complete in memory
+          tma_wait_group<kLag - 1>();
+          if (j - (kLag - 1) >= 0) publish_if_last(j - (kLag - 1));
+        }
       }
+      tma_wait_group<0>();
+      for (int j = max(0, total - (kLag - 1)); j < total; ++j) publish_if_last(j);
     }
+    __syncthreads();
     // my shard may be overwritten only after every peer has copied it
     nnbcomm::block_barrier(p.peers, p.rank, p.world, 1, me, G, p.epoch, p.comm_status);
   } else if (warp == 0) {

@@ -28,6 +28,7 @@ class Linear(nn.Module):
         super().__init__()
         self.in_features, self.out_features, self.impl = in_features, out_features, impl
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        nn.init.normal_(self.weight, std=0.02)  # the model re-initialises every weight in reset_parameters()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.weight, impl=self.impl)
@@ -100,27 +101,35 @@ class Attention(nn.Module):
         if self.tp is not None:
             # sequence parallel: x holds 1/tp of the tokens; gather them, attend over the local heads,
             # and reduce-scatter the row-parallel projection's partial sums back to token shards
+            if self.tp.fused_tp is not None:
+                from nanonemo_b200.parallel.tp_fused import column_parallel_linear, row_parallel_linear
+
+                ft = self.tp.fused_tp  # the gather and the scatter happen inside the two GEMM kernels
+                qkv = column_parallel_linear(x, self.wqkv.weight, ft).view(self.tp.B, self.tp.T, -1)
+                y = self._attend(None, cos, sin, qkv=qkv, project=False)
+                return row_parallel_linear(y.reshape(-1, y.shape[-1]), self.wo.weight, ft)
             full = self.tp.gather_tokens(x).view(self.tp.B, self.tp.T, -1)
             return self.tp.scatter_tokens(self._attend(full, cos, sin).reshape(-1, x.shape[-1]))
         return self._attend(x, cos, sin)
 
-    def _attend(self, x, cos, sin):
-        B, T, _ = x.shape
+    def _attend(self, x, cos, sin, qkv=None, project=True):
         H, KVH, hd = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = self.wqkv(x)  # (B, T, (H + 2 KVH) hd)
+        if qkv is None:
+            qkv = self.wqkv(x)  # (B, T, (H + 2 KVH) hd)
+        B, T, _ = qkv.shape
         if self.rope_impl == "sm100" or self.attn_impl == "sm100":
             # Packed path: RoPE rewrites the Q and K columns of the packed projection in one
             # launch, attention reads Q/K/V heads from it through strides and each query head
             # reads its own KV head directly (no repeat_interleave, no transposes).
             qkv = ops.rope_qkv(qkv, cos, sin, H, KVH, hd, impl=self.rope_impl)
             y = ops.attention_packed(qkv, H, KVH, hd, impl=self.attn_impl, backend=self.backend)
-            return self.wo(y)
+            return self.wo(y) if project else y
         q, k, v = qkv.split((self.q_dim, self.kv_dim, self.kv_dim), dim=-1)
         q = apply_rope(q.view(B, T, H, hd).transpose(1, 2), cos, sin)
         k = apply_rope(k.view(B, T, KVH, hd).transpose(1, 2), cos, sin)
         v = v.view(B, T, KVH, hd).transpose(1, 2)
-        y = ops.attention_torch(q, k, v, self.backend)  # (B, H, T, hd)
-        return self.wo(y.transpose(1, 2).reshape(B, T, -1))
+        y = ops.attention_torch(q, k, v, self.backend).transpose(1, 2).reshape(B, T, -1)  # (B, T, H hd)
+        return self.wo(y) if project else y
 
 
 def silu_mul(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
@@ -144,6 +153,12 @@ class MLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None:
+            if self.tp.fused_tp is not None:
+                from nanonemo_b200.parallel.tp_fused import column_parallel_linear, row_parallel_linear
+
+                ft = self.tp.fused_tp
+                act = ops.swiglu_packed(column_parallel_linear(x, self.w_gu.weight, ft), impl=self.act_impl)
+                return row_parallel_linear(act, self.w_down.weight, ft)
             full = self.tp.gather_tokens(x)
             return self.tp.scatter_tokens(self.w_down(ops.swiglu_packed(self.w_gu(full), impl=self.act_impl)))
         return self.w_down(ops.swiglu_packed(self.w_gu(x), impl=self.act_impl))

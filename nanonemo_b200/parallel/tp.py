@@ -14,8 +14,9 @@ the flattened (B*T) token axis, which makes every gather / scatter a contiguous 
 parameters live in a ``FlatParams`` store so clipping and AdamW are the fused flat kernels; and the
 operators on local tensors (norm, RoPE, attention, SwiGLU, GEMMs) are the same sm100 kernels as on
 one GPU — the reference has to force its ``torch`` norms and loss under TP (tp.py:37-38).
-With ``comm="fused"`` the all-gather / reduce-scatter of activations run as this framework's
-peer-pointer kernels over symmetric staging buffers; otherwise torch.distributed is used.
+With ``comm="fused"`` (and the sm100 GEMM) the four block linears run as single kernels that do the
+collective themselves (parallel/tp_fused.py: all-gather -> GEMM and GEMM -> reduce-scatter over peer
+memory); the embedding / head / loss collectives and the CPU path use torch.distributed.
 """
 
 import torch
@@ -27,17 +28,15 @@ from nanonemo_b200.parallel.strategy import LocalStrategy
 
 # ----------------------------------------------------------------------------- collectives with autograd
 class TPContext:
-    def __init__(self, group, rank: int, world: int, device, fused_comm=None):
+    def __init__(self, group, rank: int, world: int, device, fused_tp=None):
         self.group, self.rank, self.world, self.device = group, rank, world, torch.device(device)
-        self.fused = fused_comm  # ActivationComm (symmetric staging + kernels) or None
+        self.fused_tp = fused_tp  # parallel.tp_fused.FusedTP: linears whose collective runs inside the GEMM kernel
         self.B = self.T = 0
         self.gloo = self.device.type != "cuda"
 
     # raw collectives on contiguous 2-D tensors, along dim 0
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
         x = x.contiguous()
-        if self.fused is not None:
-            return self.fused.all_gather(x)
         out = torch.empty((x.shape[0] * self.world, *x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x, group=self.group)
         return out
@@ -45,8 +44,6 @@ class TPContext:
     def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
         x = x.contiguous()
         n = x.shape[0] // self.world
-        if self.fused is not None and x.dtype in (torch.float32,):
-            return self.fused.reduce_scatter(x)
         if self.gloo:
             x = x.clone()
             dist.all_reduce(x, group=self.group)
@@ -283,5 +280,14 @@ def build_tp(model_cfg, cfg, d):
     tp = TPContext(dist.group.WORLD, dist.get_rank(), world, d.device)
     model, step_model = build_model(model_cfg, cfg, d.device)
     shard_model_(model, tp)
+    from nanonemo_b200.parallel.symm import fused_available
+
+    tokens = cfg.micro_batch * cfg.seq_len
+    if (fused_available(d, cfg.comm) and model_cfg.resolved().linear_impl == "sm100" and cfg.precision in ("bf16", "fp16")
+            and tokens % (128 * world) == 0):
+        from nanonemo_b200.parallel.tp_fused import FusedTP
+
+        dt = torch.bfloat16 if cfg.precision == "bf16" else torch.float16
+        tp.fused_tp = FusedTP(d.device, dist.group.WORLD, tp.rank, world, tokens, model_cfg.d_model, dt)
     store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg))
     return TPStrategy(model, tp, store, step_model)

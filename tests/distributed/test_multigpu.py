@@ -41,8 +41,9 @@ def run(tmp_path, name, nproc, *overrides, loss="sm100", embed="sm100", port=295
     ("ddp", ("train.comm=nccl",), "sm100", "sm100"),
     ("fsdp", ("train.comm=fused", "train.fsdp_prefetch=true"), "sm100", "sm100"),
     ("fsdp", ("train.comm=nccl",), "sm100", "sm100"),
-    ("tp", (), "torch", "torch"),
-], ids=["ddp_fused", "ddp_nccl", "fsdp_fused", "fsdp_nccl", "tp"])
+    ("tp", ("train.comm=nccl",), "torch", "torch"),
+    ("tp", ("train.comm=fused",), "torch", "torch"),
+], ids=["ddp_fused", "ddp_nccl", "fsdp_fused", "fsdp_nccl", "tp_nccl", "tp_fused"])
 def test_two_gpus_track_one_gpu(tmp_path, par, extra, loss, embed):
     single = run(tmp_path, "one", 1, "train.parallel=none", loss=loss, embed=embed)
     multi = run(tmp_path, "two", 2, f"train.parallel={par}", *extra, loss=loss, embed=embed)
