@@ -100,9 +100,11 @@ def main(a):
         d = distributed.init()
         torch.distributed.barrier()
     model_cfg = ModelConfig(attn_backend="mem_efficient")
+    par = getattr(a, "parallel", "ddp") if world > 1 else "none"
+    dp = 1 if par == "tp" else world  # the reference's TP uses the whole world as one replica
     cfg = TrainConfig(data_dir=str(data_root), out_dir=str(data_root / "run"), seq_len=seq, micro_batch=micro,
-                      global_batch_tokens=micro * seq * world, precision="bf16", compile="default",
-                      parallel="ddp" if world > 1 else "none")
+                      global_batch_tokens=micro * seq * dp, precision="bf16", compile="default", parallel=par,
+                      fsdp_prefetch=(par == "fsdp"))
     t0 = time.perf_counter()
     try:
         r = benchmark(model_cfg, cfg, steps=a.steps, trials=1, warmup_steps=a.warmup)
@@ -124,8 +126,9 @@ def main(a):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random token ids in [0, 50257) in the reference shard format; random-init weights",
             "impl": "reference",
-            "config": {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)", "global_batch": micro * world,
-                       "seq_len": seq, "micro_batch_per_gpu": micro, "parallelism": f"dp{world}",
+            "config": {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)", "global_batch": micro * dp,
+                       "seq_len": seq, "micro_batch_per_gpu": micro,
+                       "parallelism": {"ddp": f"dp{world}", "none": "dp1", "fsdp": f"fsdp{world}", "tp": f"tp{world}+sp"}[par],
                        "stack": "torch.compile default + mem_efficient SDPA + torch DDP/NCCL + foreach AdamW",
                        "l2": "no flush: per-step working set is far larger than the 126 MB L2"},
             # The reference's benchmark() times its real train_step: every step includes the pinned

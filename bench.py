@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--kernels", default="sm100", choices=["sm100", "torch"],
                     help="operator implementation of this framework's arm (torch = the oracle path)")
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp", "tp"],
+                    help="layout for N > 1 (the headline number is ddp; fsdp / tp give the other BASELINE configs)")
     ap.add_argument("--set", nargs="*", default=[], metavar="section.key=value")
     return ap.parse_args()
 
@@ -69,9 +71,13 @@ def run_ours(a):
     if a.kernels == "sm100" and not _lib.available():
         raise SystemExit("the kernel library is not built: python -c 'import __graft_entry__ as g; g.build()'")
     model_cfg = ModelConfig.sm100() if a.kernels == "sm100" else ModelConfig(attn_backend="mem_efficient")
+    par = a.parallel if world > 1 else "none"
+    if par == "tp":  # vocab-parallel embedding / loss run on the PyTorch operators; one replica = the whole group
+        model_cfg = ModelConfig.sm100(loss_kernel="torch", embed_kernel="torch") if a.kernels == "sm100" else model_cfg
+    dp = 1 if par == "tp" else world
     cfg = TrainConfig(data_dir="synthetic", out_dir="runs/bench", seq_len=SEQ_LEN, micro_batch=a.micro_batch,
-                      global_batch_tokens=a.micro_batch * SEQ_LEN * world, total_tokens=10**12, precision="bf16",
-                      parallel="ddp" if world > 1 else "none", ddp_bucket_mb=100.0, eval_every=10**9)
+                      global_batch_tokens=a.micro_batch * SEQ_LEN * dp, total_tokens=10**12, precision="bf16",
+                      parallel=par, ddp_bucket_mb=100.0, fsdp_prefetch=True, eval_every=10**9)
     model_cfg, cfg = apply_overrides(model_cfg, cfg, a.set)
 
     # the clock sampler starts first so that it is already delivering samples when the timed region begins
@@ -141,8 +147,8 @@ def run_ours(a):
             "dtype": "bf16", "data": "synthetic uniform-random token ids in [0, 50257); random-init weights",
             "impl": "ours", "kernels": a.kernels,
             "config": {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)",
-                       "global_batch": cfg.micro_batch * world, "seq_len": cfg.seq_len, "micro_batch_per_gpu": cfg.micro_batch,
-                       "parallelism": f"dp{world}", "optimizer": "AdamW + clip 1.0, fp32 master weights",
+                       "global_batch": cfg.micro_batch * dp, "seq_len": cfg.seq_len, "micro_batch_per_gpu": cfg.micro_batch,
+                       "parallelism": {"ddp": f"dp{world}", "none": "dp1", "fsdp": f"fsdp{world}", "tp": f"tp{world}+sp"}[par], "optimizer": "AdamW + clip 1.0, fp32 master weights",
                        "l2": "no flush: per-step working set (0.46 GB weights + ~10 GB activations) is far larger than the 126 MB L2"},
             "mfu_vs_nominal_2250": value / world * flops_tok / 2250e12,
             "loss_last": loss_dev,

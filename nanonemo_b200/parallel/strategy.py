@@ -32,6 +32,41 @@ class LocalStrategy:
     def sync_ctx(self, last: bool):
         return nullcontext()
 
+    def graphed_micro_step(self, x, y, amp_dtype, accum: int):
+        """Forward + backward of one micro-batch replayed from a CUDA graph (single GPU): the whole
+        micro-batch becomes one launch, which is what matters when the batch is small and the step is
+        bound by launch overhead (the reference's ``compile: reduce-overhead`` stage). The first calls
+        run eagerly (warm-up), the next one is captured, later ones copy the batch into the static
+        input buffers and replay. Gradients accumulate into the flat gradient buffer as usual."""
+        st = self.__dict__.setdefault("_graph", {"calls": 0})
+        key = (tuple(x.shape), amp_dtype, accum)
+        if st.get("key") not in (None, key):
+            raise RuntimeError("cuda_graph: the micro-batch shape changed after capture")
+
+        def run(a, b):
+            with torch.autocast("cuda", dtype=amp_dtype, enabled=amp_dtype is not None), self.fwd_ctx():
+                _, loss = self.step_model(a, b)
+            loss = loss / accum
+            loss.backward()
+            return loss.detach()
+
+        if "graph" in st:
+            st["x"].copy_(x)
+            st["y"].copy_(y)
+            st["graph"].replay()
+            return st["loss"]
+        st["calls"] += 1
+        if st["calls"] <= 3:  # eager warm-up: allocator, kernel attributes, status buffers
+            return run(x, y)
+        st["key"], st["x"], st["y"] = key, x.clone(), y.clone()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            st["loss"] = run(st["x"], st["y"])
+        st["graph"] = graph
+        graph.replay()  # capturing records the work without running it: run this micro-batch now
+        return st["loss"]
+
     def full_loss(self, loss: torch.Tensor) -> torch.Tensor:
         return loss
 

@@ -104,7 +104,11 @@ def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) 
     if cfg.parallel == "none":
         model, step_model = build_model(model_cfg, cfg, d.device)
         store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg)) if wants_store(model_cfg, cfg, d.device) else None
-        return LocalStrategy(model, store, step_model)
+        strategy = LocalStrategy(model, store, step_model)
+        # CUDA graphs: `cuda_graph: true`, or the reference's `compile: reduce-overhead` when the sm100 kernels run
+        strategy.use_cuda_graph = d.device.startswith("cuda") and store is not None and (
+            cfg.cuda_graph or (cfg.compile == "reduce-overhead" and step_model is model))
+        return strategy
     if cfg.parallel == "ddp":
         from nanonemo_b200.parallel.ddp import DDPStrategy
         from nanonemo_b200.parallel.symm import make_grad_allreduce
@@ -144,6 +148,10 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
     loss_sum = None
     for i in range(accum):
         x, y = loader.next_batch()
+        if getattr(strategy, "use_cuda_graph", False):
+            loss = strategy.graphed_micro_step(x, y, amp_dtype, accum)
+            loss_sum = loss.clone() if loss_sum is None else loss_sum + loss
+            continue
         with strategy.sync_ctx(i == accum - 1), strategy.loss_ctx():
             with torch.autocast(x.device.type, dtype=amp_dtype, enabled=amp_dtype is not None), strategy.fwd_ctx():
                 _, loss = model(x, y)

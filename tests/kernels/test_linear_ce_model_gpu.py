@@ -96,3 +96,16 @@ def test_sm100_training_tracks_torch_training(tmp_path):
         out[name] = [r["loss"] for r in train(mc, tc, device="cuda:0") if "loss" in r]
     assert out["sm100"] == pytest.approx(out["torch"], abs=2e-2)
     assert out["sm100"][-1] < out["sm100"][0]
+
+
+def test_cuda_graph_training_matches_eager(tmp_path):
+    from nanonemo_b200.models.config import ModelConfig
+    from nanonemo_b200.train.config import TrainConfig
+    from nanonemo_b200.train.trainer import train
+
+    out = {}
+    for name, graph in (("eager", False), ("graph", True)):
+        tc = TrainConfig(data_dir="synthetic", out_dir=str(tmp_path / name), seq_len=256, micro_batch=2, global_batch_tokens=1024,
+                         total_tokens=1024 * 10, peak_lr=1e-3, precision="bf16", eval_every=100, eval_batches=1, cuda_graph=graph)
+        out[name] = [r["loss"] for r in train(ModelConfig.sm100(**SMALL), tc, device="cuda:0") if "loss" in r]
+    assert out["graph"] == pytest.approx(out["eager"], abs=2e-2)
