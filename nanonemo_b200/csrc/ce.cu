@@ -43,6 +43,8 @@ template <typename T>
 __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
                                                                 float* __restrict__ loss_rows, int V, long long ld,
                                                                 float grad_scale) {
+  extern __shared__ uint8_t s_occupancy_pad[];  // sized by the launcher to cap resident blocks per SM (see nnb_ce_inplace)
+  (void)s_occupancy_pad;
   __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
   constexpr float kLog2e = 1.4426950408889634f;
   const long long row = blockIdx.x;
@@ -119,8 +121,18 @@ extern "C" int nnb_ce_inplace(void* logits, const void* targets, void* loss_rows
   NNB_REQUIRE(V % 8 == 0 && V > 0, "ce: V=%d must be a positive multiple of 8", V);
   NNB_REQUIRE(ld % 8 == 0 && nnb_aligned16(logits), "ce: logits rows must be 16-byte aligned");
   if (R == 0) return 0;
+  // The second sweep must hit L2: keep the rows in flight (resident blocks x row bytes) well below the L2 size by
+  // padding each block's dynamic shared memory so that only a few blocks fit per SM.
+  int l2 = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+  const long long row_bytes = (long long)V * 2;
+  int per_sm = (int)(((long long)l2 / 2) / (row_bytes * nnb_num_sms()));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+  size_t pad = 0;  // 47 KB of padding (no opt-in needed) leaves room for 4 blocks per SM
+  if (per_sm < 8) pad = (size_t)min(47 * 1024, (220 * 1024) / per_sm);
   NNB_DISPATCH_16(dtype, T, {
-    ce_inplace_kernel<T><<<(unsigned)R, kCeThreads, 0, st>>>((T*)logits, (const long long*)targets, (float*)loss_rows, V, ld, grad_scale);
+    ce_inplace_kernel<T><<<(unsigned)R, kCeThreads, pad, st>>>((T*)logits, (const long long*)targets, (float*)loss_rows, V, ld, grad_scale);
   });
   NNB_LAUNCH_OK("ce_inplace");
   return 0;

@@ -180,7 +180,7 @@ extern "C" int nnb_add_rmsnorm_fwd(const void* x, const void* delta, const void*
   return 0;
 }
 
-extern "C" int nnb_rmsnorm_bwd_blocks() { return 2 * nnb_num_sms(); }
+extern "C" int nnb_rmsnorm_bwd_blocks() { return 4 * nnb_num_sms(); }
 
 template <typename TX, typename TD, typename TY>
 static int rmsnorm_bwd_t(const void* dy, const void* h, const float* rstd, const float* w, const void* dres, void* dx,
@@ -192,7 +192,8 @@ static int rmsnorm_bwd_t(const void* dy, const void* h, const float* rstd, const
     if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -3; \
     k<<<blocks, 256, smem, st>>>((const TY*)dy, (const TX*)h, rstd, w, (const TX*)dres, (TX*)dx, (TD*)ddelta, partial, M, N); \
   }
-  if (N <= 1024) NNB_RMS_BWD(4)
+  if (N <= 768) NNB_RMS_BWD(3)   // one row fits 3 chunks per lane: fewer registers, more resident warps
+  else if (N <= 1024) NNB_RMS_BWD(4)
   else NNB_RMS_BWD(8)
 #undef NNB_RMS_BWD
   return 0;

@@ -41,7 +41,13 @@ class NanoNemo(nn.Module):
         tied embedding/head weight is complete only after the embedding backward (`_tied_embedding`)."""
         w = self.tok_emb.weight
         w._tied_embedding = True
-        w._manual_ready = self.embed_impl == "sm100"
+        # Two contributions: the head (loss) and the embedding. Autograd accumulates a leaf only after ALL
+        # its backward edges have run, so if either contribution flows through autograd its accumulate hook
+        # is the completion signal; only when both are written straight into the flat buffer does the
+        # embedding backward (the last node of the graph) report the weight itself.
+        head_direct = self.loss_impl == "sm100" or self.lm_head.impl != "torch"
+        embed_direct = self.embed_impl == "sm100" or self.tp is not None
+        w._manual_ready = head_direct and embed_direct
         for m in self.modules():
             if isinstance(m, Linear) and m.impl != "torch" and m.weight is not w:
                 m.weight._manual_ready = True

@@ -110,7 +110,7 @@ class DDPStrategy(LocalStrategy):
     def _on_grad(self, p, manual: bool = False):
         # Parameters whose gradient is written straight into the flat buffer by an sm100 backward
         # (p._manual_ready) report readiness themselves; autograd's hook for them is ignored.
-        if not self._sync or (getattr(p, "_manual_ready", False) and not manual):
+        if not self._sync or getattr(p, "_manual_ready", False) != manual:  # one reporting channel per parameter
             return
         b = self._bucket_of[id(p)]
         b.pending -= 1

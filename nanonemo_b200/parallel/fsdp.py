@@ -53,6 +53,7 @@ class FSDPStrategy(LocalStrategy):
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.dp_rank, self.dp_world = self.rank, self.world
+        self.loss_ctx = nullcontext
         self.device = torch.device(d.device)
         self.cuda = self.device.type == "cuda"
         self.param_dtype = _DT[param_dtype]
@@ -249,7 +250,7 @@ class FSDPStrategy(LocalStrategy):
             self._gather(self.units[i - 1])
 
     def _on_grad(self, u, p, manual):
-        if getattr(p, "_manual_ready", False) and not manual:
+        if getattr(p, "_manual_ready", False) != manual:  # one reporting channel per parameter
             return
         if p.grad is not None and p.grad.data_ptr() != p._main_grad.data_ptr():
             p._main_grad.add_(p.grad)  # 16-bit gathered parameters: autograd produced a 16-bit grad
@@ -278,6 +279,10 @@ class FSDPStrategy(LocalStrategy):
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
+    def reduce_sumsq(self, sumsq):
+        dist.all_reduce(sumsq, group=self.group)
+        return sumsq
+
     def step(self, opt, grad_clip, scaler=None, keep_grads=False):
         assert scaler is None, "the sharded strategies run in bf16 / fp32 (no loss scaler)"
         if not hasattr(self, "_opt"):
@@ -287,7 +292,7 @@ class FSDPStrategy(LocalStrategy):
             sumsq = self.sumsq.clone()
         else:
             sumsq = self.shard_grad.pow(2).sum()
-        dist.all_reduce(sumsq, group=self.group)
+        sumsq = self.reduce_sumsq(sumsq)
         norm = sumsq.sqrt()
         self.opt_step += 1
         g0 = opt.param_groups[0]
@@ -352,6 +357,68 @@ class FSDPStrategy(LocalStrategy):
             self.opt_step = int(float(state["optim"]["step"]))
             self.wire.copy_(self.shard)
         self.gather_all(initial=not self.fused)
+
+
+class FSDPTPStrategy(FSDPStrategy):
+    """2-D mesh: the model has been sliced for tensor parallelism (`tp`), and the slice is fully sharded
+    over the data-parallel group. Differences from plain FSDP: parameters replicated inside the TP group
+    (norm weights) saw only 1/tp of the tokens, so their reduced gradient shards are summed over the TP
+    group; the global gradient norm counts them once; checkpoints gather over both mesh axes."""
+
+    name = "fsdp_tp"
+
+    def __init__(self, model, d, tp, *args, **kw):
+        self.tp = tp
+        super().__init__(model, d, *args, **kw)
+        from nanonemo_b200.parallel.tp import shard_rule
+
+        # ranges of this rank's shard buffers that hold TP-replicated parameters
+        self.rep_ranges = []
+        for u in self.units:
+            per = (u.hi - u.lo) // self.world
+            s0, _ = self._shard_range(u)
+            lo_own, hi_own = self.rank * per, (self.rank + 1) * per
+            for n, p, o in zip(u.names, u.params, u.offsets):
+                if shard_rule(n) is None:
+                    a, b = max(o, lo_own), min(o + p.numel(), hi_own)
+                    if a < b:
+                        self.rep_ranges.append((s0 + a - lo_own, s0 + b - lo_own))
+
+    def finish_grads(self):
+        super().finish_grads()
+        if self.rep_ranges:
+            flat = torch.cat([self.shard_grad[a:b] for a, b in self.rep_ranges])
+            dist.all_reduce(flat, group=self.tp.group)
+            o = 0
+            for a, b in self.rep_ranges:
+                self.shard_grad[a:b].copy_(flat[o:o + b - a])
+                o += b - a
+
+    def reduce_sumsq(self, sumsq):
+        if self.fused:  # the reduce-scatter kernel summed the squares before the TP reduction: recompute
+            sumsq = self.shard_grad.pow(2).sum()
+        rep = sum((self.shard_grad[a:b].pow(2).sum() for a, b in self.rep_ranges), torch.zeros((), device=sumsq.device))
+        total = sumsq - rep * ((self.tp.world - 1) / self.tp.world)  # replicated entries are identical on tp ranks
+        dist.all_reduce(total)  # over the whole mesh
+        return total
+
+    def state_for_checkpoint(self, opt):
+        from nanonemo_b200.parallel.tp import tp_full_tensor
+
+        st = super().state_for_checkpoint(opt)
+        cfg = self.model.cfg
+        full = lambda d_: {n: tp_full_tensor(n, t, self.tp, cfg) for n, t in d_.items()}
+        return {"model": full(st["model"]), "optim": {"exp_avg": full(st["optim"]["exp_avg"]),
+                                                        "exp_avg_sq": full(st["optim"]["exp_avg_sq"]), "step": st["optim"]["step"]}}
+
+    def load_from_checkpoint(self, opt, state):
+        from nanonemo_b200.parallel.tp import tp_local_slice
+
+        cfg = self.model.cfg
+        loc = lambda d_: {n: tp_local_slice(n, t, self.tp, cfg) for n, t in d_.items()}
+        super().load_from_checkpoint(opt, {"model": loc(state["model"]),
+                                           "optim": {"exp_avg": loc(state["optim"]["exp_avg"]),
+                                                     "exp_avg_sq": loc(state["optim"]["exp_avg_sq"]), "step": state["optim"]["step"]}})
 
 
 def build_fsdp(model_cfg, cfg, d):

@@ -177,6 +177,7 @@ def shard_model_(model, tp: TPContext):
         a.tp = m.tp = tp
     model.tok_emb.weight.data = model.tok_emb.weight[r * Vl:(r + 1) * Vl].contiguous()
     model.tp, model.vocab_start = tp, r * Vl
+    model._mark_gradient_paths()  # the vocabulary-parallel embedding writes its gradient directly: re-derive who reports the tied weight
     return model
 
 
@@ -220,34 +221,10 @@ class TPStrategy(LocalStrategy):
 
     # checkpoint state: gather the shards back to full tensors
     def _full(self, name, local):
-        rule, tp, cfg = shard_rule(name), self.tp, self.model.cfg
-        if rule is None:
-            return local.detach().clone()
-        parts = [torch.empty_like(local) for _ in range(tp.world)]
-        dist.all_gather(parts, local.detach().contiguous(), group=tp.group)
-        hd, W = cfg.head_dim, tp.world
-        if rule == "qkv":
-            q, kv = cfg.n_heads // W * hd, cfg.n_kv_heads // W * hd
-            return torch.cat([p[:q] for p in parts] + [p[q:q + kv] for p in parts] + [p[q + kv:] for p in parts])
-        if rule == "gu":
-            f = cfg.d_ff // W
-            return torch.cat([p[:f] for p in parts] + [p[f:] for p in parts])
-        return torch.cat(parts, dim=rule)
+        return tp_full_tensor(name, local, self.tp, self.model.cfg)
 
     def _local(self, name, full):
-        rule, tp, cfg = shard_rule(name), self.tp, self.model.cfg
-        if rule is None:
-            return full
-        r, W, hd = tp.rank, tp.world, cfg.head_dim
-        if rule == "qkv":
-            Q, KV = cfg.n_heads * hd, cfg.n_kv_heads * hd
-            q, kv = Q // W, KV // W
-            return torch.cat((full[r * q:(r + 1) * q], full[Q + r * kv:Q + (r + 1) * kv], full[Q + KV + r * kv:Q + KV + (r + 1) * kv]))
-        if rule == "gu":
-            Fd, f = cfg.d_ff, cfg.d_ff // W
-            return torch.cat((full[r * f:(r + 1) * f], full[Fd + r * f:Fd + (r + 1) * f]))
-        n = full.shape[rule] // W
-        return full.narrow(rule, r * n, n)
+        return tp_local_slice(name, full, self.tp, self.model.cfg)
 
     def state_for_checkpoint(self, opt):
         base = super().state_for_checkpoint(opt)
@@ -267,27 +244,92 @@ class TPStrategy(LocalStrategy):
         super().load_from_checkpoint(opt, local)
 
 
-def build_tp(model_cfg, cfg, d):
-    from nanonemo_b200.parallel.flat import FlatParams
-    from nanonemo_b200.train.trainer import build_model, shadow_dtype
+def tp_full_tensor(name, local, tp, cfg):
+    """All-gather a tensor-parallel shard of parameter `name` back to the full tensor."""
+    rule = shard_rule(name)
+    if rule is None:
+        return local.detach().clone()
+    parts = [torch.empty_like(local) for _ in range(tp.world)]
+    dist.all_gather(parts, local.detach().contiguous(), group=tp.group)
+    hd, W = cfg.head_dim, tp.world
+    if rule == "qkv":
+        q, kv = cfg.n_heads // W * hd, cfg.n_kv_heads // W * hd
+        return torch.cat([p[:q] for p in parts] + [p[q:q + kv] for p in parts] + [p[q + kv:] for p in parts])
+    if rule == "gu":
+        f = cfg.d_ff // W
+        return torch.cat([p[:f] for p in parts] + [p[f:] for p in parts])
+    return torch.cat(parts, dim=rule)
 
-    if cfg.parallel == "fsdp_tp":
-        raise NotImplementedError("the 2-D fsdp_tp mesh is not built yet")
-    world = dist.get_world_size()
-    tp_size = cfg.tp_size or world
-    if tp_size != world:
-        raise ValueError("parallel=tp uses the whole world as the tensor-parallel group (tp_size must equal world)")
-    tp = TPContext(dist.group.WORLD, dist.get_rank(), world, d.device)
-    model, step_model = build_model(model_cfg, cfg, d.device)
-    shard_model_(model, tp)
+
+def tp_local_slice(name, full, tp, cfg):
+    """This rank's tensor-parallel shard of the full tensor of parameter `name`."""
+    rule = shard_rule(name)
+    if rule is None:
+        return full
+    r, W, hd = tp.rank, tp.world, cfg.head_dim
+    if rule == "qkv":
+        Q, KV = cfg.n_heads * hd, cfg.n_kv_heads * hd
+        q, kv = Q // W, KV // W
+        return torch.cat((full[r * q:(r + 1) * q], full[Q + r * kv:Q + (r + 1) * kv], full[Q + KV + r * kv:Q + KV + (r + 1) * kv]))
+    if rule == "gu":
+        Fd, f = cfg.d_ff, cfg.d_ff // W
+        return torch.cat((full[r * f:(r + 1) * f], full[Fd + r * f:Fd + (r + 1) * f]))
+    n = full.shape[rule] // W
+    return full.narrow(rule, r * n, n)
+
+
+def _maybe_fuse(tp, model_cfg, cfg, d, group):
     from nanonemo_b200.parallel.symm import fused_available
 
     tokens = cfg.micro_batch * cfg.seq_len
     if (fused_available(d, cfg.comm) and model_cfg.resolved().linear_impl == "sm100" and cfg.precision in ("bf16", "fp16")
-            and tokens % (128 * world) == 0):
+            and tokens % (128 * tp.world) == 0):
         from nanonemo_b200.parallel.tp_fused import FusedTP
 
         dt = torch.bfloat16 if cfg.precision == "bf16" else torch.float16
-        tp.fused_tp = FusedTP(d.device, dist.group.WORLD, tp.rank, world, tokens, model_cfg.d_model, dt)
-    store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg))
-    return TPStrategy(model, tp, store, step_model)
+        tp.fused_tp = FusedTP(d.device, group, tp.rank, tp.world, tokens, model_cfg.d_model, dt)
+
+
+def build_tp(model_cfg, cfg, d):
+    """parallel=tp: the whole world is one tensor-parallel group. parallel=fsdp_tp: a 2-D mesh, consecutive
+    groups of tp_size ranks are tensor parallel and the parameters each of them holds are fully sharded
+    over the world / tp_size data-parallel ranks with the same position in their group."""
+    from nanonemo_b200.parallel.flat import FlatParams
+    from nanonemo_b200.train.trainer import build_model, shadow_dtype
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if cfg.parallel == "tp":
+        if (cfg.tp_size or world) != world:
+            raise ValueError("parallel=tp uses the whole world as the tensor-parallel group; use fsdp_tp for a 2-D mesh")
+        tp = TPContext(dist.group.WORLD, rank, world, d.device)
+        model, step_model = build_model(model_cfg, cfg, d.device)
+        shard_model_(model, tp)
+        _maybe_fuse(tp, model_cfg, cfg, d, dist.group.WORLD)
+        store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg))
+        return TPStrategy(model, tp, store, step_model)
+
+    tps = cfg.tp_size
+    if world % tps:
+        raise ValueError(f"tp_size {tps} does not divide the world size {world}")
+    tp_group = dp_group = None
+    for g in range(world // tps):  # every rank creates every group, in the same order
+        ranks = list(range(g * tps, (g + 1) * tps))
+        grp = dist.new_group(ranks)
+        if rank in ranks:
+            tp_group = grp
+    for i in range(tps):
+        ranks = list(range(i, world, tps))
+        grp = dist.new_group(ranks)
+        if rank in ranks:
+            dp_group = grp
+    tp = TPContext(tp_group, rank % tps, tps, d.device)
+    model, step_model = build_model(model_cfg, cfg, d.device)
+    shard_model_(model, tp)
+    _maybe_fuse(tp, model_cfg, cfg, d, tp_group)
+    from nanonemo_b200.parallel.fsdp import FSDPTPStrategy
+
+    pd = cfg.fsdp_param_dtype
+    if pd == "fp32" and model_cfg.uses_sm100("linear_impl") and cfg.precision in ("bf16", "fp8"):
+        pd = "bf16"
+    return FSDPTPStrategy(model, d, tp, pd, cfg.fsdp_reshard_after_forward, cfg.fsdp_prefetch, cfg.comm, group=dp_group,
+                          step_model=step_model, precision=cfg.precision)

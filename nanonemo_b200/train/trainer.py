@@ -124,7 +124,7 @@ def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) 
         return build_fsdp(model_cfg, cfg, d)
     from nanonemo_b200.parallel.tp import build_tp
 
-    return build_tp(model_cfg, cfg, d)
+    return build_tp(model_cfg, cfg, d)  # tp and the 2-D fsdp_tp mesh
 
 
 def build_scaler(cfg: TrainConfig, device: str, sharded: bool = False):

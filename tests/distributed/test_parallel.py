@@ -80,6 +80,15 @@ def test_ddp_checkpoint_resumes_under_tp(tmp_path, single):
     assert first + rest == pytest.approx(single, abs=1e-4)
 
 
+def test_2d_mesh_fsdp_x_tp_matches_one_process_and_resumes_elsewhere(tmp_path, single):
+    """4 ranks = 2 data-parallel (fully sharded) x 2 tensor-parallel; then its checkpoint resumes under DDP on 2 ranks."""
+    losses, _ = run(tmp_path, "mesh", 4, "train.tp_size=2", "train.parallel=fsdp_tp")
+    assert losses == pytest.approx(single, abs=1e-4)
+    first, out = run(tmp_path, "a", 4, "train.tp_size=2", "train.parallel=fsdp_tp", "train.max_steps=3")
+    rest, _ = run(tmp_path, "b", 2, "train.parallel=ddp", f"train.resume_from={out / 'ckpt'}")
+    assert first + rest == pytest.approx(single, abs=1e-4)
+
+
 def test_a_rank_that_never_joins_times_out_on_the_host(tmp_path):
     """Failure detection without touching a GPU: one of two gloo ranks exits before the rendezvous
     completes its first collective; the survivor's collective must end with an error within the
