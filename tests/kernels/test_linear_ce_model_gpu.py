@@ -94,8 +94,7 @@ def test_sm100_training_tracks_torch_training(tmp_path):
         tc = TrainConfig(data_dir="synthetic", out_dir=str(tmp_path / name), seq_len=256, micro_batch=4, global_batch_tokens=2048,
                          total_tokens=2048 * 12, peak_lr=1e-3, precision="bf16", eval_every=100, eval_batches=1)
         out[name] = [r["loss"] for r in train(mc, tc, device="cuda:0") if "loss" in r]
-    assert out["sm100"] == pytest.approx(out["torch"], abs=2e-2)
-    assert out["sm100"][-1] < out["sm100"][0]
+    assert out["sm100"] == pytest.approx(out["torch"], abs=2e-2)  # uniform-random tokens: the loss itself stays near ln V
 
 
 def test_cuda_graph_training_matches_eager(tmp_path):
