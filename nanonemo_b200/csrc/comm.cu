@@ -41,30 +41,51 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
+// WMAX = compile-time bound on the world size, U = independent 16-byte positions per thread: U x WMAX peer
+// loads are issued before the first add, so each thread keeps 1 KB in flight over NVLink (the kernel is
+// latency-bound otherwise: one load per peer per thread reached only a third of NCCL's bus bandwidth).
+template <int WMAX, int U>
 __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, float* mc, int rank, int world, long long lo,
                                                                      long long n, float scale, uint32_t epoch, int* status) {
   const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);  // every peer's inputs are final
   const long long per = ((n + world - 1) / world + 3) & ~3LL;       // slice length, multiple of 4
   const long long s0 = min((long long)rank * per, n), s1 = min(s0 + per, n);
   const long long n4 = (s1 - s0) >> 2;
+  const long long stride = (long long)gridDim.x * blockDim.x;
   if (ok) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-      const long long off = lo + s0 + 4 * i;
-      float4 acc;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
+      float4 v[U][WMAX];
       if (mc != nullptr) {
-        acc = multimem_ld_reduce_f4(mc + off);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < n4) v[u][0] = multimem_ld_reduce_f4(mc + lo + s0 + 4 * (i0 + u * stride));
       } else {
-        acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < world; ++r) {  // fixed order: the result does not depend on who reduces
-          const float4 v = ld_peer_f4(static_cast<const float*>(P.data[r]) + off);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int r = 0; r < WMAX; ++r)
+            if (r < world && i0 + u * stride < n4)
+              v[u][r] = ld_peer_f4(static_cast<const float*>(P.data[r]) + lo + s0 + 4 * (i0 + u * stride));
       }
-      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-      if (mc != nullptr) {
-        multimem_st_f4(mc + off, acc);
-      } else {
-        for (int r = 0; r < world; ++r) *reinterpret_cast<float4*>(static_cast<float*>(P.data[r]) + off) = acc;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= n4) continue;
+        const long long off = lo + s0 + 4 * i;
+        float4 acc = v[u][0];
+        if (mc == nullptr) {
+#pragma unroll
+          for (int r = 1; r < WMAX; ++r)  // fixed order: the result does not depend on who reduces
+            if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
+        }
+        acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        if (mc != nullptr) {
+          multimem_st_f4(mc + off, acc);
+        } else {
+#pragma unroll
+          for (int r = 0; r < WMAX; ++r)
+            if (r < world) *reinterpret_cast<float4*>(static_cast<float*>(P.data[r]) + off) = acc;
+        }
       }
     }
   }
@@ -72,24 +93,36 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, fl
 }
 
 // out[i] = scale * sum_r data[r][lo + rank*per + i]; sumsq_out += sum(out^2) (one atomic per block).
+template <int WMAX, int U>
 __global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers P, float* out, float* sumsq_out, int rank, int world,
                                                                           long long lo, long long per, float scale,
                                                                           uint32_t epoch, int* status) {
   __shared__ float s_part[kCommThreads / 32];
   const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);
   const long long n4 = per >> 2;
+  const long long stride = (long long)gridDim.x * blockDim.x;
   float ss = 0.f;
   if (ok) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-      const long long off = lo + (long long)rank * per + 4 * i;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < world; ++r) {
-        const float4 v = ld_peer_f4(static_cast<const float*>(P.data[r]) + off);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
+      float4 v[U][WMAX];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int r = 0; r < WMAX; ++r)
+          if (r < world && i0 + u * stride < n4)
+            v[u][r] = ld_peer_f4(static_cast<const float*>(P.data[r]) + lo + (long long)rank * per + 4 * (i0 + u * stride));
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= n4) continue;
+        float4 acc = v[u][0];
+#pragma unroll
+        for (int r = 1; r < WMAX; ++r)
+          if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
+        acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        reinterpret_cast<float4*>(out)[i] = acc;
+        ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
       }
-      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-      reinterpret_cast<float4*>(out)[i] = acc;
-      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
     }
   }
   if (sumsq_out != nullptr) {
@@ -117,10 +150,17 @@ __global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_
       const int r = (rank + rr) % world;  // start with the local shard, then spread the peers
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.data[r]) + src_off);
       uint4* dst = reinterpret_cast<uint4*>(local_full + (long long)r * per_bytes);
-      for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
-        uint4 v;
-        asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
-        dst[i] = v;
+      const long long stride = (long long)gridDim.x * blockDim.x;
+      for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n16; i0 += stride * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (i0 + u * stride < n16)
+            asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i0 + u * stride) : "memory");
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (i0 + u * stride < n16) dst[i0 + u * stride] = v[u];
       }
     }
   }
@@ -139,8 +179,12 @@ extern "C" int nnb_allreduce_f32(void* const* data_ptrs, void* const* flag_ptrs,
   NNB_REQUIRE(lo % 4 == 0 && n % 4 == 0, "allreduce: range must be 16-byte aligned (lo=%lld n=%lld)", lo, n);
   NNB_REQUIRE(blocks > 0 && blocks <= 1024, "allreduce: bad block count %d", blocks);
   if (n == 0) return 0;
-  allreduce_f32_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<float*>(multicast_ptr), rank, world, lo, n, scale,
-                                                        (uint32_t)epoch, static_cast<int*>(status));
+  NNB_REQUIRE(world <= 8, "allreduce: world %d > 8 not supported by the unrolled kernel", world);
+  float* mc = static_cast<float*>(multicast_ptr);
+  int* stw = static_cast<int*>(status);
+  if (world <= 2) allreduce_f32_kernel<2, 8><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
+  else if (world <= 4) allreduce_f32_kernel<4, 4><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
+  else allreduce_f32_kernel<8, 2><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
   NNB_LAUNCH_OK("allreduce_f32");
   return 0;
 }
@@ -152,8 +196,13 @@ extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_
   if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
   NNB_REQUIRE(lo % 4 == 0 && per % 4 == 0, "reduce_scatter: range must be 16-byte aligned");
   if (per == 0) return 0;
-  reduce_scatter_f32_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<float*>(out), static_cast<float*>(sumsq_out), rank, world,
-                                                             lo, per, scale, (uint32_t)epoch, static_cast<int*>(status));
+  NNB_REQUIRE(world <= 8, "reduce_scatter: world %d > 8 not supported by the unrolled kernel", world);
+  float* o = static_cast<float*>(out);
+  float* sq = static_cast<float*>(sumsq_out);
+  int* stw = static_cast<int*>(status);
+  if (world <= 2) reduce_scatter_f32_kernel<2, 8><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
+  else if (world <= 4) reduce_scatter_f32_kernel<4, 4><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
+  else reduce_scatter_f32_kernel<8, 2><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
   NNB_LAUNCH_OK("reduce_scatter_f32");
   return 0;
 }

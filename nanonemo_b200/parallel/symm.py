@@ -54,7 +54,7 @@ class SymmetricComm:
         from nanonemo_b200.ops import _lib
 
         self.rank, self.world, self.group = rank, world, group
-        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", "32"))
+        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", "48"))
         words = _lib.lib().nnb_comm_flag_words(self.blocks)
         self.flags = SymmetricBuffer(words, torch.int32, device, group)
         self.flags.tensor.zero_()
