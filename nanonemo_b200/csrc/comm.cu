@@ -167,7 +167,25 @@ __global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_
   block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);  // shards may be rewritten once everybody has copied them
 }
 
+// Exercises the bounded wait: a "world" of two ranks whose flag buffers are both this GPU's buffer, so the
+// slot that the (absent) second rank would write is never written. The wait gives up after `poll_limit`
+// polls, records the status words and the kernel returns normally; the context stays usable.
+__global__ void timeout_probe_kernel(Peers P, uint32_t epoch, uint32_t poll_limit, int* status, int* result) {
+  const bool ok = block_barrier(P, 0, 2, 0, 0, 1, epoch, status, poll_limit);
+  if (threadIdx.x == 0) *result = ok ? 1 : -1;
+}
+
 }  // namespace
+
+extern "C" int nnb_comm_timeout_probe(void* flags, void* status, void* result, int epoch, int poll_limit, cudaStream_t st) {
+  Peers P;
+  void* both[2] = {flags, flags};
+  if (fill_peers(P, nullptr, both, 2) != 0) return -1;
+  NNB_REQUIRE(poll_limit > 0 && poll_limit <= (1 << 22), "timeout_probe: poll_limit out of range");
+  timeout_probe_kernel<<<1, 64, 0, st>>>(P, (uint32_t)epoch, (uint32_t)poll_limit, static_cast<int*>(status), static_cast<int*>(result));
+  NNB_LAUNCH_OK("timeout_probe");
+  return 0;
+}
 
 // Flag buffer requirement: uint32 [2 phases][blocks][16] per rank, zero before the first call.
 extern "C" int nnb_comm_flag_words(int blocks) { return 2 * blocks * kMaxWorld; }

@@ -37,7 +37,7 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
 // a wait ran out (status = {code, rank, peer, block, epoch} recorded once). Call from all threads of
 // the block (needs at least `world` threads).
 __device__ __forceinline__ bool block_barrier(const Peers& P, int rank, int world, int phase, int slot_block, int n_slot_blocks,
-                                              uint32_t epoch, int* status) {
+                                              uint32_t epoch, int* status, uint32_t poll_limit = kPollLimit) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __threadfence_system();
@@ -49,7 +49,7 @@ __device__ __forceinline__ bool block_barrier(const Peers& P, int rank, int worl
     const uint32_t* mine = P.flags[rank] + slot + peer;
     uint32_t polls = 0;
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {  // signed distance tolerates wrap-around
-      if (++polls > kPollLimit) {
+      if (++polls > poll_limit) {
         s_fail = 1;
         if (status != nullptr && atomicCAS(status, 0, 10 + phase) == 0) {
           status[1] = rank; status[2] = peer; status[3] = slot_block; status[4] = (int)epoch;

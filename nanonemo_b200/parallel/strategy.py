@@ -21,7 +21,7 @@ class LocalStrategy:
 
     def __init__(self, model: nn.Module, store=None, step_model: nn.Module | None = None):
         self.model = model
-        self.step_model = step_model or model
+        self.step_model = step_model if step_model is not None else model  # (a compiled module has no truth value)
         self.store = store
         self.dp_rank, self.dp_world = 0, 1
         self.loss_ctx = nullcontext

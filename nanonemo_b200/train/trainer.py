@@ -107,7 +107,7 @@ def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) 
         strategy = LocalStrategy(model, store, step_model)
         # CUDA graphs: `cuda_graph: true`, or the reference's `compile: reduce-overhead` when the sm100 kernels run
         strategy.use_cuda_graph = d.device.startswith("cuda") and store is not None and (
-            cfg.cuda_graph or (cfg.compile == "reduce-overhead" and step_model is model))
+            cfg.cuda_graph or cfg.compile == "reduce-overhead")
         return strategy
     if cfg.parallel == "ddp":
         from nanonemo_b200.parallel.ddp import DDPStrategy

@@ -14,8 +14,7 @@ def main(argv=None):
     root = Path(argv[0]) if argv else next(iter(sorted(Path("results/ladder").glob("*"))), None)
     if root is None or not root.exists():
         raise SystemExit("no results under results/ladder: run scripts/bench_train.py on the stage configs first")
-    rows = sorted((json.loads(p.read_text()), p.stem) for p in root.glob("*.json"))
-    rows.sort(key=lambda r: r[1])
+    rows = [(json.loads(p.read_text()), p.stem) for p in sorted(root.glob("*.json"))]
     print(f"| stage | tok/s (median) | step ms | vs previous | MFU | peak GB | flags |\n|---|---|---|---|---|---|---|")
     prev = None
     for r, name in rows:
