@@ -83,7 +83,9 @@ def build_model(model_cfg: ModelConfig, cfg: TrainConfig, device: str):
                                                         "loss_kernel", "linear_impl", "embed_kernel"))
     if cfg.compile is None or any_sm100:
         return model, model
-    return model, torch.compile(model, mode=None if cfg.compile in ("default", "reduce-overhead") else cfg.compile)
+    # PyTorch-operator path: Inductor, and for reduce-overhead its own CUDA-graph trees (gradients accumulate into
+    # the static flat gradient views outside the compiled region)
+    return model, torch.compile(model, mode=None if cfg.compile == "default" else cfg.compile)
 
 
 def build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) -> LocalStrategy:
@@ -106,7 +108,7 @@ def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) 
         store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg)) if wants_store(model_cfg, cfg, d.device) else None
         strategy = LocalStrategy(model, store, step_model)
         # CUDA graphs: `cuda_graph: true`, or the reference's `compile: reduce-overhead` when the sm100 kernels run
-        strategy.use_cuda_graph = d.device.startswith("cuda") and store is not None and (
+        strategy.use_cuda_graph = d.device.startswith("cuda") and store is not None and step_model is model and (
             cfg.cuda_graph or cfg.compile == "reduce-overhead")
         return strategy
     if cfg.parallel == "ddp":
@@ -148,6 +150,7 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
     loss_sum = None
     for i in range(accum):
         x, y = loader.next_batch()
+        torch.compiler.cudagraph_mark_step_begin()  # no-op unless a compiled model replays CUDA graphs
         if getattr(strategy, "use_cuda_graph", False):
             loss = strategy.graphed_micro_step(x, y, amp_dtype, accum)
             loss_sum = loss.clone() if loss_sum is None else loss_sum + loss
