@@ -36,24 +36,11 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One block per row, two sweeps. Sweep 1 reads the row from HBM and keeps a running (max, sum-exp)
-// per thread; sweep 2 re-reads it — a row is ~100 KB and a few hundred rows are in flight, far below
-// the 126 MB L2, so the second read does not reach HBM — and overwrites it with the gradient.
+// Sweep 1 of a row: every thread keeps a running (max, sum-exp) over its 16-byte vectors, then the block combines the
+// pairs. Returns the row's (max, sum of exp(x - max)) to every thread.
 template <typename T>
-__global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
-                                                                float* __restrict__ loss_rows, int V, long long ld,
-                                                                float grad_scale) {
-  extern __shared__ uint8_t s_occupancy_pad[];  // sized by the launcher to cap resident blocks per SM (see nnb_ce_inplace)
-  (void)s_occupancy_pad;
-  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+__device__ __forceinline__ float2 row_max_sumexp(const T* __restrict__ x, int nvec, float* s_m, float* s_s) {
   constexpr float kLog2e = 1.4426950408889634f;
-  const long long row = blockIdx.x;
-  T* x = logits + row * ld;
-  const int nvec = V >> 3;
-  const long long tgt = targets[row];
-  const bool valid = tgt >= 0 && tgt < V;
-  const float x_t = valid ? to_f32(x[tgt]) : 0.f;
-
   float m = -INFINITY, s = 0.f;
   for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
     const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
@@ -92,9 +79,13 @@ __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ 
   float S = 0.f;
 #pragma unroll
   for (int i = 0; i < kCeThreads / 32; ++i) S += s_m[i] == -INFINITY ? 0.f : s_s[i] * exp2f((s_m[i] - M) * kLog2e);
-  const float lse = M + logf(S);
-  if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
-  const float gs = valid ? grad_scale : 0.f;  // ignored rows contribute no gradient
+  return make_float2(M, S);
+}
+
+// Sweep 2 of a row: overwrite it with (softmax - onehot) * gs, softmax = exp(x - lse). tgt outside [0, 8 nvec) = no onehot here.
+template <typename T>
+__device__ __forceinline__ void row_write_grad(T* __restrict__ x, int nvec, long long tgt, float lse, float gs) {
+  constexpr float kLog2e = 1.4426950408889634f;
   const float lb = lse * kLog2e;
   for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
     uint4 raw = reinterpret_cast<const uint4*>(x)[v];
@@ -110,6 +101,68 @@ __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ 
     }
     reinterpret_cast<uint4*>(x)[v] = raw;
   }
+}
+
+// One block per row, two sweeps. Sweep 1 reads the row from HBM; sweep 2 re-reads it — a row is ~100 KB and a few hundred
+// rows are in flight, far below the 126 MB L2, so the second read does not reach HBM — and overwrites it with the gradient.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
+                                                                float* __restrict__ loss_rows, int V, long long ld,
+                                                                float grad_scale) {
+  extern __shared__ uint8_t s_occupancy_pad[];  // sized by the launcher to cap resident blocks per SM (see nnb_ce_inplace)
+  (void)s_occupancy_pad;
+  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+  const long long row = blockIdx.x;
+  T* x = logits + row * ld;
+  const long long tgt = targets[row];
+  const bool valid = tgt >= 0 && tgt < V;
+  const float x_t = valid ? to_f32(x[tgt]) : 0.f;
+  const float2 ms = row_max_sumexp<T>(x, V >> 3, s_m, s_s);
+  const float lse = ms.x + logf(ms.y);
+  if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
+  row_write_grad<T>(x, V >> 3, tgt, lse, valid ? grad_scale : 0.f);  // ignored rows contribute no gradient
+}
+
+// Vocabulary-parallel variant, first half: this rank's slice of the row -> stats[row] = (max, sum-exp, target logit or 0).
+// `targets` are GLOBAL ids; this rank owns columns [v0, v0 + V).
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads) ce_stats_kernel(const T* __restrict__ logits, const long long* __restrict__ targets,
+                                                              float* __restrict__ stats, int V, long long ld, long long v0) {
+  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+  const long long row = blockIdx.x;
+  const T* x = logits + row * ld;
+  const long long tgt = targets[row] - v0;
+  const float2 ms = row_max_sumexp<T>(x, V >> 3, s_m, s_s);
+  if (threadIdx.x == 0) {
+    stats[row * 4 + 0] = ms.x;
+    stats[row * 4 + 1] = ms.y;
+    stats[row * 4 + 2] = (tgt >= 0 && tgt < V) ? to_f32(x[tgt]) : 0.f;
+    stats[row * 4 + 3] = 0.f;
+  }
+}
+
+// Second half: stats_all [world, R, 4] holds every rank's (max, sum-exp, target logit); each block combines them to the
+// row's global logsumexp, writes the row loss (identical on all ranks) and overwrites this rank's slice with the gradient.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads) ce_grad_vp_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
+                                                                const float* __restrict__ stats_all, float* __restrict__ loss_rows,
+                                                                int V, long long ld, long long v0, long long v_total, int world,
+                                                                long long R, float grad_scale) {
+  const long long row = blockIdx.x;
+  T* x = logits + row * ld;
+  const long long tg = targets[row];
+  const bool valid = tg >= 0 && tg < v_total;
+  float M = -INFINITY;
+  for (int r = 0; r < world; ++r) M = fmaxf(M, stats_all[((long long)r * R + row) * 4]);
+  float S = 0.f, x_t = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float* st = stats_all + ((long long)r * R + row) * 4;
+    S += st[0] == -INFINITY ? 0.f : st[1] * expf(st[0] - M);
+    x_t += st[2];
+  }
+  const float lse = M + logf(S);
+  if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
+  row_write_grad<T>(x, V >> 3, valid ? tg - v0 : -1, lse, valid ? grad_scale : 0.f);
 }
 
 }  // namespace
@@ -135,5 +188,35 @@ extern "C" int nnb_ce_inplace(void* logits, const void* targets, void* loss_rows
     ce_inplace_kernel<T><<<(unsigned)R, kCeThreads, pad, st>>>((T*)logits, (const long long*)targets, (float*)loss_rows, V, ld, grad_scale);
   });
   NNB_LAUNCH_OK("ce_inplace");
+  return 0;
+}
+
+
+// Vocabulary-parallel cross-entropy in two launches with one small all-gather of `stats` between them (done by the caller).
+// logits: this rank's [R, V] slice of the row (columns v0 .. v0+V of v_total); targets: global ids.
+extern "C" int nnb_ce_stats(const void* logits, const void* targets, void* stats, long long R, int V, long long ld,
+                            long long v0, int dtype, cudaStream_t st) {
+  NNB_REQUIRE(V % 8 == 0 && V > 0, "ce_stats: V=%d must be a positive multiple of 8", V);
+  NNB_REQUIRE(ld % 8 == 0 && nnb_aligned16(logits), "ce_stats: logits rows must be 16-byte aligned");
+  if (R == 0) return 0;
+  NNB_DISPATCH_16(dtype, T, {
+    ce_stats_kernel<T><<<(unsigned)R, kCeThreads, 0, st>>>((const T*)logits, (const long long*)targets, (float*)stats, V, ld, v0);
+  });
+  NNB_LAUNCH_OK("ce_stats");
+  return 0;
+}
+
+extern "C" int nnb_ce_grad_vp(void* logits, const void* targets, const void* stats_all, void* loss_rows, long long R, int V,
+                              long long ld, long long v0, long long v_total, int world, float grad_scale, int dtype,
+                              cudaStream_t st) {
+  NNB_REQUIRE(V % 8 == 0 && V > 0, "ce_grad_vp: V=%d must be a positive multiple of 8", V);
+  NNB_REQUIRE(ld % 8 == 0 && nnb_aligned16(logits), "ce_grad_vp: logits rows must be 16-byte aligned");
+  NNB_REQUIRE(world >= 1 && world <= 64, "ce_grad_vp: world=%d out of range", world);
+  if (R == 0) return 0;
+  NNB_DISPATCH_16(dtype, T, {
+    ce_grad_vp_kernel<T><<<(unsigned)R, kCeThreads, 0, st>>>((T*)logits, (const long long*)targets, (const float*)stats_all,
+                                                             (float*)loss_rows, V, ld, v0, v_total, world, R, grad_scale);
+  });
+  NNB_LAUNCH_OK("ce_grad_vp");
   return 0;
 }

@@ -35,14 +35,21 @@ constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
 constexpr int kStagingBytes = 2 * BM * 128;  // two 128-row x 128-byte staging tiles
 
-template <int BN>
+// MX = block-scaled e4m3 operands (MXFP8): a stage is still 128 bytes of K per row (128 elements instead of 64) plus the
+// e8m0 scales of its rows (512 bytes per 128 rows: 4 K-blocks of 32 x 128 rows); the scales take 8 more TMEM columns.
+template <int BN, bool MX = false>
 struct Cfg {
   static constexpr int kStageBytesA = BM * BK * 2;
   static constexpr int kStageBytesB = BN * BK * 2;
-  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 4 : 6);
-  static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;  // two accumulators; allocations are powers of two
+  static constexpr int kOperandBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kSfBytesA = MX ? 512 : 0, kSfBytesB = MX ? (BN / 128) * 512 : 0;
+  static constexpr int kStageBytes = kOperandBytes + (MX ? 1024 : 0);  // stage stride keeps the 1024-byte alignment
+  static constexpr int kTxBytes = kOperandBytes + kSfBytesA + kSfBytesB;
+  static constexpr int kStages = MX ? 5 : ((BN == 256) ? 4 : (BN == 192 ? 4 : 6));
+  static constexpr int kSfCol = 2 * BN;  // TMEM columns [2 BN, 2 BN + 4) scales of A, [2 BN + 4, 2 BN + 8) scales of B
+  static constexpr int kTmemCols = (2 * BN + (MX ? 8 : 0) <= 256) ? 256 : 512;  // allocations are powers of two
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(!MX || BN == 128, "the block-scaled path is built for 128-wide tiles (two accumulators + scales must fit 512 columns)");
 };
 
 struct Params {
@@ -52,6 +59,9 @@ struct Params {
   int out_f32;          // output dtype: 0 = 16-bit (same as inputs), 1 = fp32
   int reduce_add;       // epilogue uses TMA reduce-add (fp32 only)
   uint32_t idesc;
+  int out_bf16;         // 16-bit output format: 1 = bf16, 0 = fp16
+  const uint8_t* sfa;   // MX: e8m0 scales of A in 512-byte chunks [m-block][k-block] (see nnb_mxfp8_quantize_sw)
+  const uint8_t* sfb;   // MX: same for the rows of B, chunk index [n / 128][k-block]
   int* status;          // device int[4]: {code, role, block, item}; code 0 = ok
   // ---- fused collectives (mode 0: none)
   //  mode 1  GEMM -> reduce-scatter: output rows are sharded over `world` ranks (mblocks_per_rank m-blocks each);
@@ -71,11 +81,12 @@ struct DMaps {
   CUtensorMap m[8];       // mode 1: one output map per rank; otherwise m[0]
 };
 
-template <int BN>
+template <int BN, bool MX>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ DMaps tmDs, const Params p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, MX>;
+  constexpr int kBlockK = MX ? 2 * BK : BK;  // elements of K per stage (always 128 bytes per row)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
@@ -225,8 +236,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; fail_role = 1; fail_item = item; break; }
           const uint32_t full = bar_full + 8 * s;
-          mbar_expect_tx(full, C::kStageBytes);
+          mbar_expect_tx(full, C::kTxBytes);
           const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes), sb = sa + C::kStageBytesA;
+          if constexpr (MX) {
+            tma_load_2d(sa, &tmA, full, kb * kBlockK, m_blk * BM);
+            tma_load_2d(sb, &tmB, full, kb * kBlockK, n_blk * BN);
+            bulk_load(sa + C::kOperandBytes, p.sfa + ((long long)m_blk * p.kblocks_total + kb) * 512, 512, full);
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              bulk_load(sa + C::kOperandBytes + 512 + 512 * j, p.sfb + ((long long)(n_blk * (BN / 128) + j) * p.kblocks_total + kb) * 512, 512, full);
+            continue;
+          }
           if (!p.a_mn) {
             tma_load_2d(sa, &tmA, full, kb * BK, m_blk * BM);
           } else {
@@ -269,9 +289,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_fence_after();
           const uint32_t sa = smem_u32(stage_base + s * C::kStageBytes), sb = sa + C::kStageBytesA;
           const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
+          if constexpr (MX) {
+            // scales of this stage: shared memory -> tensor memory (tcgen05 operations of one thread execute in order, so the
+            // copy neither overtakes the previous stage's MMAs nor is overtaken by the ones below)
+            const uint32_t sf_tmem = tmem_base + C::kSfCol;
+            tmem_cp_32x128b_warpx4(sf_tmem, make_smem_desc_noswizzle(sa + C::kOperandBytes, 0, 128));
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16(d_tmem, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int j = 0; j < BN / 128; ++j)
+              tmem_cp_32x128b_warpx4(sf_tmem + 4 + 4 * j, make_smem_desc_noswizzle(sa + C::kOperandBytes + 512 + 512 * j, 0, 128));
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k)  // 4 x K = 32 (32 bytes of every 128-byte row); scale byte k of each column
+              umma_mxf8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), p.idesc | (k << 4) | (k << 29),
+                        sf_tmem | (k << 30), (sf_tmem + 4) | (k << 30), (kb > kb0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              umma_f16(d_tmem, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(bar_empty + 8 * s);  // the stage is free once these MMAs have read it
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);  // accumulator complete
@@ -331,7 +365,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld_32x32b_x32(t_row + col0, r0);
           tmem_ld_32x32b_x32(t_row + col0 + 32, r1);
           tmem_ld_wait();
-          const bool is_bf16 = ((p.idesc >> 7) & 7) == 1;
+          const bool is_bf16 = p.out_bf16 != 0;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             uint32_t w[4];
@@ -396,18 +430,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN>
+template <int BN, bool MX = false>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const DMaps& tmDs, const Params& p, int grid, cudaStream_t st) {
-  auto kern = gemm_tcgen05_kernel<BN>;
+  auto kern = gemm_tcgen05_kernel<BN, MX>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes) != cudaSuccess) {
-      nnb_set_error("gemm: cannot reserve %d bytes of shared memory", Cfg<BN>::kSmemBytes);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, MX>::kSmemBytes) != cudaSuccess) {
+      nnb_set_error("gemm: cannot reserve %d bytes of shared memory", Cfg<BN, MX>::kSmemBytes);
       return -3;
     }
     configured = true;
   }
-  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, st>>>(tmA, tmB, tmDs, p);
+  kern<<<grid, kThreads, Cfg<BN, MX>::kSmemBytes, st>>>(tmA, tmB, tmDs, p);
   return 0;
 }
 
@@ -482,6 +516,7 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   p.out_f32 = out_f32 ? 1 : 0;
   p.reduce_add = (accumulate || p.k_splits > 1 || mode == 1) ? 1 : 0;
   p.idesc = sm100::make_idesc_f16(dtype == NNB_BF16 ? 1 : 0, p.a_mn, p.b_mn, BM, BN);
+  p.out_bf16 = dtype == NNB_BF16 ? 1 : 0;
   p.status = static_cast<int*>(status);
   p.mode = mode;
 
@@ -570,4 +605,68 @@ extern "C" int nnb_ag_gemm_bf16(void* const* a_ptrs, const void* B, void* D, voi
                                 long long ldb, long long ldd, int b_mn, int dtype, void* status, cudaStream_t st) {
   CommArgs c{2, world, rank, gather_ctas, a_ptrs, flag_ptrs, local_flags, comm_status, epoch};
   return gemm_impl(a_ptrs[rank], B, D, M, N, K, K, ldb, ldd, 0, b_mn, dtype, 0, 0, 1, 0, 0, status, &c, st);
+}
+
+// MXFP8 GEMM on the block-scaled tensor-core path: D[M, N] (+)= (A * sfa) (B * sfb)^T.
+//   A: e4m3 bytes [M, K] row-major (lda bytes per row), B: e4m3 bytes [N, K]; both contract along their rows (K-major).
+//   sfa / sfb: e8m0 scales, one per 32 K-elements of every row, in the chunked layout written by nnb_mxfp8_quantize_sw:
+//   chunk [row / 128][k / 128] of 512 bytes, scale of (row, k-block) at byte (row % 32) * 16 + ((row % 128) / 32) * 4 + (k / 32) % 4.
+//   D: bf16 (out_f32 = 0) or fp32 (out_f32 = 1; accumulate adds into D; split-K partial tiles are reduce-added).
+// M, N and K must be multiples of 128. The reference has no FP8 GEMM of its own (it defers to Transformer Engine,
+// nanonemo/te/__init__.py:20-39).
+extern "C" int nnb_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* D, int M, int N, int K,
+                              long long lda, long long ldb, long long ldd, int out_f32, int accumulate, int k_splits, int max_ctas,
+                              void* status, cudaStream_t st) {
+  constexpr int BN = 128, KB = 2 * BK;
+  NNB_REQUIRE(M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 128 == 0,
+              "gemm_mxfp8: M=%d, N=%d, K=%d must be positive multiples of 128", M, N, K);
+  NNB_REQUIRE(!accumulate || out_f32, "gemm_mxfp8: accumulate needs an fp32 output");
+  NNB_REQUIRE(lda % 16 == 0 && ldb % 16 == 0 && nnb_aligned16(A) && nnb_aligned16(B) && nnb_aligned16(sfa) && nnb_aligned16(sfb),
+              "gemm_mxfp8: operands and scales must be 16-byte aligned with row strides that are multiples of 16");
+  const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
+  Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.m_blocks = M / BM;
+  p.n_blocks = N / BN;
+  p.kblocks_total = K / KB;
+  int splits = 1;
+  if (out_f32) {
+    if (k_splits > 0) splits = k_splits;
+    else {
+      const long long tiles = (long long)p.m_blocks * p.n_blocks;
+      const int s_max = max(1, min(32, p.kblocks_total / 4));
+      double best = 1e30;
+      for (int sp = 1; sp <= s_max; ++sp) {
+        const double cost = (double)((tiles * sp + sms - 1) / sms) / sp + 0.002 * sp;
+        if (cost < best - 1e-9) { best = cost; splits = sp; }
+      }
+    }
+    splits = max(1, min(splits, p.kblocks_total));
+  }
+  p.kblocks_per_split = (p.kblocks_total + splits - 1) / splits;
+  p.k_splits = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.out_f32 = out_f32 ? 1 : 0;
+  p.reduce_add = (accumulate || p.k_splits > 1) ? 1 : 0;
+  p.idesc = sm100::make_idesc_mxf8(BM, BN);
+  p.out_bf16 = 1;
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.status = static_cast<int*>(status);
+  CUtensorMap tmA, tmB;
+  DMaps tmDs;
+  if (!nnb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, lda, BM, KB, "gemm_mxfp8 A")) return -4;
+  if (!nnb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, N, K, ldb, BN, KB, "gemm_mxfp8 B")) return -4;
+  const CUtensorMapDataType d_dt = out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int d_bytes = out_f32 ? 4 : 2, d_box = out_f32 ? 32 : 64;
+  if (!nnb_make_tmap_2d(&tmDs.m[0], d_dt, d_bytes, D, M, N, ldd * d_bytes, BM, d_box, "gemm_mxfp8 D")) return -4;
+  for (int r = 1; r < 8; ++r) tmDs.m[r] = tmDs.m[0];
+  if (out_f32 && !accumulate && p.k_splits > 1) {
+    if (ldd == N) cudaMemsetAsync(D, 0, (size_t)M * N * 4, st);
+    else cudaMemset2DAsync(D, ldd * 4, 0, (size_t)N * 4, M, st);
+  }
+  const int items = p.m_blocks * p.n_blocks * p.k_splits;
+  const int rc = launch<BN, true>(tmA, tmB, tmDs, p, min(items, sms), st);
+  if (rc != 0) return rc;
+  NNB_LAUNCH_OK("gemm_mxfp8");
+  return 0;
 }

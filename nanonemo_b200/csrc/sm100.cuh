@@ -229,6 +229,40 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Block-scaled 8-bit MMA (MXFP8): D[tmem] (+)= (A * sfa) (B * sfb)^T with one e8m0 scale per 32 contraction elements of every
+// row; K = 32 per instruction. The scales sit in tensor memory (32-bit column c, lane l holds the 4 scale bytes of row
+// 32 c' + l of 4 consecutive K blocks, replicated over the four lane quarters); the byte used is picked by the scale ids in
+// the instruction descriptor AND by bits 30-31 of the scale addresses.
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                          uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// Shared memory -> tensor memory copy of 32 rows x 16 bytes, broadcast to the four lane quarters: the scale factors of 128
+// rows x 4 K-blocks (row r at byte (r % 32) * 16 + (r / 32) * 4 of the 512-byte chunk) land in 4 columns.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Descriptor of an unswizzled K-major block whose 8-row groups of 16-byte rows are `sbo_bytes` apart (128 when contiguous).
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version for sm_100; layout type 0 = no swizzle
+  return d;
+}
+// Instruction descriptor for kind::mxf8f6f4.block_scale with e4m3 operands (format 0), K-major, e8m0 scales (bit 23);
+// the scale ids (bits 4-5 for B, 29-30 for A) are OR-ed in per instruction.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int M, int N) {
+  return ((uint32_t)(N >> 3) << 17) | (1u << 23) | ((uint32_t)(M >> 4) << 24);
+}
+// Plain bulk copy global -> shared with mbarrier completion (16-byte aligned addresses and size).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

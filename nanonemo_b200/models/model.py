@@ -103,6 +103,10 @@ class NanoNemo(nn.Module):
         for block in self.blocks:
             x, delta = block(x, self.rope_cos, self.rope_sin, delta)
         h = tp.gather_tokens(self.norm_out(x, delta)[0])
+        if targets is not None and self.loss_impl == "sm100":
+            from nanonemo_b200.ops.linear_ce import vocab_parallel_linear_cross_entropy
+
+            return None, vocab_parallel_linear_cross_entropy(h, self.lm_head.weight, targets.reshape(-1), tp, self.vocab_start)
         logits = self.lm_head(h)  # [B*T, V / tp]
         if targets is None:
             return logits, None

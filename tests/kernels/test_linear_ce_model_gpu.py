@@ -30,6 +30,39 @@ def test_linear_ce_loss_and_grads(N, D, V, chunk):
         assert err <= 3e-2 * want.abs().max().item() + 1e-5, err
 
 
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_vocab_parallel_linear_ce_over_emulated_ranks(world):
+    """Every 'rank' holds V/world rows of the head; the stats exchange is emulated by running the ranks' first halves,
+    concatenating their stats, then running the second halves. Loss and gradients must equal the unsharded fp32 loss."""
+    from nanonemo_b200.ops import linear_ce
+    from nanonemo_b200.ops.gemm import check_status, gemm
+
+    torch.manual_seed(world)
+    N, D, V = 640, 128, 2048
+    Vl = V // world
+    x = (torch.randn(N, D, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(V, D, device=DEV) * 0.2).bfloat16()
+    t = torch.randint(0, V, (N,), device=DEV)
+    t[5] = -100  # ignored row
+    logits = [gemm(x, w[r * Vl:(r + 1) * Vl].contiguous()) for r in range(world)]
+    ref_logits = torch.cat([l.float() for l in logits], dim=1).requires_grad_()
+    stats = [torch.empty(N, 4, device=DEV) for _ in range(world)]
+    for r in range(world):
+        linear_ce._ce_stats(logits[r], t, stats[r], r * Vl)
+    stats_all = torch.cat(stats)
+    losses = [torch.empty(N, device=DEV) for _ in range(world)]
+    for r in range(world):
+        linear_ce._ce_grad_vp(logits[r], t, stats_all, losses[r], r * Vl, V, world, 1.0 / N)
+    check_status()
+    ref_rows = F.cross_entropy(ref_logits, t, reduction="none", ignore_index=-100)
+    (ref_rows.sum() / N).backward()
+    for r in range(world):
+        torch.testing.assert_close(losses[r], ref_rows.detach(), rtol=1e-4, atol=1e-4)
+    got = torch.cat([l.float() for l in logits], dim=1)
+    assert (got - ref_logits.grad).abs().max().item() <= 1e-2 * ref_logits.grad.abs().max().item() + 1e-7
+    assert got[5].abs().max().item() == 0.0
+
+
 def test_linear_ce_peak_memory_is_far_below_unfused():
     from nanonemo_b200 import ops
 
