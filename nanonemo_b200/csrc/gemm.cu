@@ -22,7 +22,10 @@
 //
 // This replaces the cuBLAS calls behind nn.Linear in the reference (nanonemo/model/layers.py:80-83,
 // 128-130); the reference ships no tensor-core GEMM of its own.
+#include <cstdlib>
+
 #include "comm.cuh"
+#include "gemm2.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -55,6 +58,7 @@ struct Cfg {
 struct Params {
   int M, N, K;
   int m_blocks, n_blocks, k_splits, kblocks_total, kblocks_per_split;
+  int group_m;          // tile order: groups of group_m m-blocks are swept n-block by n-block (1 = row by row)
   int a_mn, b_mn;       // operand majors
   int out_f32;          // output dtype: 0 = 16-bit (same as inputs), 1 = fp32
   int reduce_add;       // epilogue uses TMA reduce-add (fp32 only)
@@ -135,6 +139,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int cta0 = (int)blockIdx.x - first_compute, nctas = (int)gridDim.x - first_compute;
   // m-block visited at position `ord`: mode 2 starts with this rank's own rows, then follows the gather order
   auto m_of = [&](int ord) { return p.mode == 2 ? (p.rank * p.mblocks_per_rank + ord) % p.m_blocks : ord; };
+  // tile index -> (position of the m-block, n-block). Consecutive tiles — the ones the persistent CTAs work on at the same
+  // time — cover group_m m-blocks x (CTAs / group_m) n-blocks, so a wave re-uses a few MB of A and B from L2 instead of
+  // streaming every n-block of B for a single m-block.
+  auto tile_coords = [&](int tile, int& m_ord, int& n_blk) {
+    const int per_group = p.group_m * p.n_blocks, g = tile / per_group, r = tile - g * per_group;
+    const int gm = min(p.group_m, p.m_blocks - g * p.group_m);
+    m_ord = g * p.group_m + r % gm;
+    n_blk = r / gm;
+  };
 
   if (p.mode == 1 && blockIdx.x == 0) {
     // every rank's output buffer has been zeroed (stream order on each rank) before anybody adds into it
@@ -219,7 +232,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int item = cta0; item < items && ok; item += nctas) {
         const int ks = item % p.k_splits, tile = item / p.k_splits;
-        const int n_blk = tile % p.n_blocks, m_blk = m_of(tile / p.n_blocks);
+        int m_ord, n_blk;
+        tile_coords(tile, m_ord, n_blk);
+        const int m_blk = m_of(m_ord);
         const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         if (p.mode == 2 && m_blk / p.mblocks_per_rank != p.rank) {
           // rows of a peer: wait until a gather CTA has landed this m-block in the local buffer
@@ -321,7 +336,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool go = p.mode != 1;  // mode 1: the first reduce waits until every rank has zeroed its output
     for (int item = cta0; item < items; item += nctas, ++tile_iter) {
       const int tile = item / p.k_splits;
-      const int n_blk = tile % p.n_blocks, m_blk = m_of(tile / p.n_blocks);
+      int m_ord, n_blk;
+      tile_coords(tile, m_ord, n_blk);
+      const int m_blk = m_of(m_ord);
       // where the tile goes: mode 1 = the owner rank's buffer (peer memory), row offset inside its shard
       const int owner = p.mode == 1 ? m_blk / p.mblocks_per_rank : 0;
       const int d_row = p.mode == 1 ? (m_blk - owner * p.mblocks_per_rank) * BM : m_blk * BM;
@@ -467,6 +484,16 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   NNB_REQUIRE(!accumulate || out_f32 || mode == 1, "gemm: accumulate needs an fp32 output");
   const CUtensorMapDataType in_dt = dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
+  // CTA-pair kernel (gemm2.cu): 256 x 256 tiles over two SMs. Measured faster than the single-CTA tiles at every shape of
+  // the 114M model (3-14 %), slower only for large cubes (8192^3), where the single-CTA raster does better.
+  static const bool pair_enabled = [] { const char* e = getenv("NANONEMO_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+  const bool big_cube = M >= 4096 && N >= 4096 && K >= 4096;
+  if (mode == 0 && (bn_hint == 512 || (bn_hint == 0 && pair_enabled && M >= 256 && N >= 256 && !big_cube))) {
+    const NnbGemm2Args g{A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, dtype, out_f32, accumulate, k_splits, max_ctas, status};
+    const int rc = nnb_gemm2_launch(g, st);
+    if (rc <= 0) return rc;  // 1 = shape not served: fall through to the single-CTA kernel
+    bn_hint = 0;
+  }
   const int m_blocks_ = (M + BM - 1) / BM;
   // Tile width: the widest tile is the most efficient per FLOP, but the number of tiles should fill whole
   // waves of `sms` persistent CTAs. cost = waves x tile width (a tile's time is proportional to its width).
@@ -511,6 +538,14 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   }
   p.kblocks_per_split = (p.kblocks_total + splits - 1) / splits;
   p.k_splits = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.group_m = 1;
+  if (mode == 0) {
+    // wave of `sms` tiles = group_m x (sms / group_m) blocks; footprint group_m BM K + (sms / group_m) BN K is least at
+    // group_m = sqrt(sms BN / BM). Only matters when one row of tiles is longer than the wave share.
+    int g = 1;
+    while ((g + 1) * (g + 1) * BM <= sms * BN) ++g;
+    if (p.n_blocks * g > sms) p.group_m = min(g, p.m_blocks);
+  }
   p.a_mn = a_mn ? 1 : 0;
   p.b_mn = b_mn ? 1 : 0;
   p.out_f32 = out_f32 ? 1 : 0;
@@ -645,6 +680,12 @@ extern "C" int nnb_gemm_mxfp8(const void* A, const void* sfa, const void* B, con
   }
   p.kblocks_per_split = (p.kblocks_total + splits - 1) / splits;
   p.k_splits = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.group_m = 1;
+  {
+    int g = 1;
+    while ((g + 1) * (g + 1) * BM <= sms * BN) ++g;
+    if (p.n_blocks * g > sms) p.group_m = min(g, p.m_blocks);
+  }
   p.out_f32 = out_f32 ? 1 : 0;
   p.reduce_add = (accumulate || p.k_splits > 1) ? 1 : 0;
   p.idesc = sm100::make_idesc_mxf8(BM, BN);

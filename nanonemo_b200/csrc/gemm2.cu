@@ -1,0 +1,390 @@
+// bf16/fp16 GEMM with CTA PAIRS on the 5th-generation tensor cores: D[M,N] (+)= A[M,K] * B[N,K]^T, fp32 accumulate.
+//
+// Two CTAs of a cluster (two SMs) own one 256 x 256 output tile. Each CTA loads its own 128 rows of A and its own
+// 128 of the 256 rows of B; ONE thread of the even ("leader") CTA issues tcgen05.mma.cta_group::2 (M = 256), which
+// reads A and B from the shared memory of both CTAs and accumulates each CTA's 128 rows into that CTA's own tensor
+// memory. Per 128 x 256 of output a CTA therefore stages 32 KB per k-block instead of the 48 KB of the single-CTA
+// kernel (gemm.cu): the L2 -> shared-memory fill, which bounds these GEMMs at K = 768..2048, drops by a third.
+// No multicast is used: every CTA fetches its own tiles; the pair is coupled only through
+//   * TMA loads of both CTAs completing on the leader's "full" barrier (cta_group::2 form of the load),
+//   * tcgen05.commit.cta_group::2 arriving on the "empty" / "accumulator full" barriers of BOTH CTAs (one commit per CTA),
+//   * the peer's epilogue warps arriving remotely on the leader's "accumulator empty" barrier.
+// Roles per CTA as in gemm.cu: warp 0 TMA producer, warp 1 MMA issuer (leader only; both allocate TMEM), warps 2..5
+// epilogue (tcgen05.ld -> swizzled staging -> TMA store / reduce-add). All waits are bounded.
+// Replaces the cuBLAS calls behind nn.Linear in the reference (nanonemo/model/layers.py:80-83, 128-130).
+#include "gemm2.cuh"
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;   // rows per CTA (256 per pair)
+constexpr int BN = 256;   // columns per pair tile; each CTA stages BN / 2 rows of B
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kStages = 6;
+constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = (BN / 2) * BK * 2, kStageBytes = kStageBytesA + kStageBytesB;
+constexpr int kStagingBytes = 2 * BM * 128;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+
+struct Params2 {
+  int M, N, K;
+  int m_pairs, n_blocks, k_splits, kblocks_total, kblocks_per_split;
+  int group_m;  // tile order: groups of group_m 256-row blocks are swept n-block by n-block
+  int a_mn, b_mn, out_f32, reduce_add, out_bf16;
+  uint32_t idesc;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// TMA tile load issued by either CTA of the pair; the bytes are counted on the LEADER's mbarrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t leader_bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on ONE mbarrier (a shared::cluster address, own or the peer's) once the pair MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmD, const Params2 p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* staging = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kStages, bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_abort = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);    // leader: its producer's expect-tx arrival (bytes of both CTAs)
+      mbar_init(bar_empty + 8 * s, 1);   // one commit per CTA
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * (kEpilogueThreads / 32));  // leader: epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    *epi_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc2(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish2();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmD);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anybody signals the peer
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int items = p.m_pairs * p.n_blocks * p.k_splits;
+  const int pair0 = (int)blockIdx.x >> 1, npairs = (int)gridDim.x >> 1;
+  int fail_role = 0, fail_item = -1;
+  // consecutive tiles (the ones the persistent pairs work on at the same time) cover group_m x (pairs / group_m) blocks
+  auto tile_coords = [&](int tile, int& m_pair, int& n_blk) {
+    const int per_group = p.group_m * p.n_blocks, g = tile / per_group, r = tile - g * per_group;
+    const int gm = min(p.group_m, p.m_pairs - g * p.group_m);
+    m_pair = g * p.group_m + r % gm;
+    n_blk = r / gm;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      const uint32_t leader_full0 = map_to_cta(bar_full, 0);  // the same barrier slot in the even CTA of the pair
+      for (int item = pair0; item < items && ok; item += npairs) {
+        const int ks = item % p.k_splits, tile = item / p.k_splits;
+        int m_pair, n_blk;
+        tile_coords(tile, m_pair, n_blk);
+        const int m_row0 = (m_pair * 2 + (int)rank) * BM;
+        const int n_row0 = n_blk * BN + (int)rank * (BN / 2);
+        const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; fail_role = 1; fail_item = item; break; }
+          const uint32_t full = bar_full + 8 * s, leader_full = leader_full0 + 8 * s;
+          if (rank == 0) mbar_expect_tx(full, 2 * kStageBytes);
+          const uint32_t sa = smem_u32(stage_base + s * kStageBytes), sb = sa + kStageBytesA;
+          if (!p.a_mn) {
+            tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, m_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, leader_full, m_row0 + j * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sb, &tmB, leader_full, kb * BK, n_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmB, leader_full, n_row0 + j * 64, kb * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      const uint32_t a_step = p.a_mn ? (16 * 128) >> 4 : 32 >> 4, b_step = p.b_mn ? (16 * 128) >> 4 : 32 >> 4;
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
+      const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_tfull = map_to_cta(bar_tfull, 1);
+      for (int item = pair0; item < items && ok; item += npairs, ++tile_iter) {
+        const int ks = item % p.k_splits;
+        const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        const uint32_t acc = tile_iter & 1, acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag)) { ok = false; fail_role = 2; fail_item = item; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) { ok = false; fail_role = 2; fail_item = item; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * kStageBytes), sb = sa + kStageBytesA;
+          const uint64_t da = make_smem_desc(sa, a_lbo, 1024), db = make_smem_desc(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16_pair(d_tmem, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(bar_empty + 8 * s);    // this CTA's stage is free once the MMAs have read it
+          umma_commit_pair(peer_empty + 8 * s);   // ... and so is the peer's
+        }
+        if (ok) {
+          umma_commit_pair(bar_tfull + 8 * acc);
+          umma_commit_pair(peer_tfull + 8 * acc);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int et = threadIdx.x - 64;
+    uint32_t tile_iter = 0, gchunk = 0;
+    int pending_stores = 0;
+    const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+    for (int item = pair0; item < items; item += npairs, ++tile_iter) {
+      const int tile = item / p.k_splits;
+      int m_pair, n_blk;
+      tile_coords(tile, m_pair, n_blk);
+      const int d_row = (m_pair * 2 + (int)rank) * BM;
+      const uint32_t acc = tile_iter & 1, acc_ph = (tile_iter >> 1) & 1;
+      const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag);
+      if (!ok) { fail_role = 3; fail_item = item; }
+      if (et == 0) *epi_abort = *abort_flag;
+      named_barrier_sync(1, kEpilogueThreads);
+      if (*epi_abort) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const int cols_per_chunk = p.out_f32 ? 32 : 64;
+      const int chunks = BN / cols_per_chunk;
+      const bool rows_live = d_row < p.M;  // an odd number of 128-row blocks leaves the peer's last block outside the matrix
+      for (int c = 0; c < chunks && rows_live; ++c) {
+        const int col0 = c * cols_per_chunk;
+        if (n_blk * BN + col0 >= p.N) break;
+        uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
+        ++gchunk;
+        if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
+        named_barrier_sync(1, kEpilogueThreads);
+        uint8_t* my_row = buf + row * 128;
+        const int sw = row & 7;
+        if (p.out_f32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + col0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        } else {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_row + col0, r0);
+          tmem_ld_32x32b_x32(t_row + col0 + 32, r1);
+          tmem_ld_wait();
+          const bool is_bf16 = p.out_bf16 != 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = (j & 3) * 8 + 2 * e;
+              const float lo = __uint_as_float(j < 4 ? r0[i] : r1[i]), hi = __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]);
+              if (is_bf16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                w[e] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                w[e] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, kEpilogueThreads);
+        if (et == 0) {
+          if (p.reduce_add) tma_reduce_add_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
+          else tma_store_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
+          tma_commit_group();
+        }
+        if (pending_stores < 2) ++pending_stores;
+      }
+      // this CTA's half of the accumulator has been read: tell the leader's MMA thread
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(bar_tempty + 8 * acc);
+        else mbar_arrive_cluster(leader_tempty + 8 * acc);
+      }
+    }
+    if (et == 0) tma_wait_group<0>();
+  }
+
+  if (fail_item >= 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, 1) == 0) {
+      p.status[1] = fail_role;
+      p.status[2] = blockIdx.x;
+      p.status[3] = fail_item;
+    }
+  }
+  // The peer's shared memory and barriers are in use until the leader's last MMA and commit have completed, and the pair
+  // frees its tensor memory together: meet before leaving.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
+  const int sms = a.max_ctas > 0 ? min(a.max_ctas, nnb_num_sms()) : nnb_num_sms();
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    cudaFuncSetAttribute(gemm2_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * (nnb_num_sms() / 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm2_tcgen05_kernel, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = 0; }
+    max_clusters = n;
+  }
+  const int pairs = min(sms / 2, max_clusters);  // persistent pairs must all be resident at once
+  if (pairs < 1 || a.M < 2 * BM || a.N < BN / 2) return 1;
+  Params2 p{};
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.m_pairs = (a.M + 2 * BM - 1) / (2 * BM);
+  p.n_blocks = (a.N + BN - 1) / BN;
+  p.kblocks_total = (a.K + BK - 1) / BK;
+  int splits = 1;
+  if (a.out_f32) {
+    if (a.k_splits > 0) splits = a.k_splits;
+    else {
+      const long long tiles = (long long)p.m_pairs * p.n_blocks;
+      const int s_max = max(1, min(32, p.kblocks_total / 4));
+      double best = 1e30;
+      for (int sp = 1; sp <= s_max; ++sp) {
+        const double cost = (double)((tiles * sp + pairs - 1) / pairs) / sp + 0.002 * sp;
+        if (cost < best - 1e-9) { best = cost; splits = sp; }
+      }
+    }
+    splits = max(1, min(splits, p.kblocks_total));
+  }
+  p.kblocks_per_split = (p.kblocks_total + splits - 1) / splits;
+  p.k_splits = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.group_m = 1;
+  {
+    int g = 1;
+    while ((g + 1) * (g + 1) * 2 * BM <= pairs * BN) ++g;  // least wave footprint: group_m = sqrt(pairs BN / (2 BM))
+    if (p.n_blocks * g > pairs) p.group_m = min(g, p.m_pairs);
+  }
+  p.a_mn = a.a_mn ? 1 : 0;
+  p.b_mn = a.b_mn ? 1 : 0;
+  p.out_f32 = a.out_f32 ? 1 : 0;
+  p.reduce_add = (a.accumulate || p.k_splits > 1) ? 1 : 0;
+  p.out_bf16 = a.dtype == NNB_BF16 ? 1 : 0;
+  p.idesc = sm100::make_idesc_f16(a.dtype == NNB_BF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN);
+  p.status = static_cast<int*>(a.status);
+  const CUtensorMapDataType in_dt = a.dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tmA, tmB, tmD;
+  if (!p.a_mn) { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, a.A, a.M, a.K, a.lda * 2, BM, BK, "gemm2 A")) return -4; }
+  else         { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, a.A, a.K, a.M, a.lda * 2, BK, 64, "gemm2 A^T")) return -4; }
+  if (!p.b_mn) { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, a.B, a.N, a.K, a.ldb * 2, BN / 2, BK, "gemm2 B")) return -4; }
+  else         { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, a.B, a.K, a.N, a.ldb * 2, BK, 64, "gemm2 B^T")) return -4; }
+  const CUtensorMapDataType d_dt = a.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : in_dt;
+  const int d_bytes = a.out_f32 ? 4 : 2, d_box = a.out_f32 ? 32 : 64;
+  if (!nnb_make_tmap_2d(&tmD, d_dt, d_bytes, a.D, a.M, a.N, a.ldd * d_bytes, BM, d_box, "gemm2 D")) return -4;
+  if (a.out_f32 && !a.accumulate && p.k_splits > 1) {
+    if (a.ldd == a.N) cudaMemsetAsync(a.D, 0, (size_t)a.M * a.N * 4, st);
+    else cudaMemset2DAsync(a.D, a.ldd * 4, 0, (size_t)a.N * 4, a.M, st);
+  }
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm2_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+      nnb_set_error("gemm2: cannot reserve %d bytes of shared memory", kSmemBytes);
+      return -3;
+    }
+    configured = true;
+  }
+  const int items = p.m_pairs * p.n_blocks * p.k_splits;
+  const int grid = 2 * min(items, pairs);
+  gemm2_tcgen05_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, tmD, p);
+  NNB_LAUNCH_OK("gemm2_tcgen05");
+  return 0;
+}

@@ -15,6 +15,13 @@ typedef CUresult (*NnbEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static inline NnbEncodeTiled nnb_encode_fn() {
+  // The encoder is a driver call and needs a current context. A thread that has only ever been handed work (an autograd
+  // worker whose device is already "current" for PyTorch) may not have bound the primary context yet: bind it once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static NnbEncodeTiled fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -20,7 +20,7 @@ def _check(out, ref, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (256, 512, 768), (384, 1280, 768), (130, 264, 72),
-                                   (1000, 768, 2048), (64, 64, 64), (4096, 768, 768)])
+                                   (1000, 768, 2048), (64, 64, 64), (4096, 768, 768), (2560, 20096, 64)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_fprop_layout(M, N, K, dtype):
     from nanonemo_b200.ops.gemm import check_status, gemm
@@ -61,6 +61,33 @@ def test_wgrad_layout_fp32_out(M, N, K, k_splits):
     gemm(at, bt, a_mn=True, b_mn=True, out=acc, accumulate=True, k_splits=k_splits)
     check_status()
     _check(acc - 1, ref, K)
+
+
+@pytest.mark.parametrize("layout", ["fprop", "dgrad", "wgrad"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 768), (1024, 2304, 768), (384, 1280, 1024), (2048, 256, 2048),
+                                   (304, 520, 136), (4096, 4352, 128)])
+def test_cta_pair_kernel(layout, M, N, K):
+    """bn=512 selects the two-SM kernel (256 x 256 tiles, tcgen05.mma.cta_group::2); ragged edges and an odd number of
+    128-row blocks (the second CTA's last block lies outside the matrix) included."""
+    from nanonemo_b200.ops.gemm import check_status, gemm
+
+    torch.manual_seed(M + N + K)
+    if layout == "fprop":
+        a, b = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()
+        out, ref = gemm(a, b, bn=512), _ref(a, b, False, False)
+    elif layout == "dgrad":
+        a, b = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(K, N, device=DEV).bfloat16()
+        out, ref = gemm(a, b, b_mn=True, bn=512), _ref(a, b, False, True)
+    else:
+        a, b = torch.randn(K, M, device=DEV).bfloat16(), torch.randn(K, N, device=DEV).bfloat16()
+        ref = _ref(a, b, True, True)
+        out = gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32, bn=512)
+        acc = torch.ones(M, N, device=DEV)
+        gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, k_splits=2 if K >= 128 else 1, bn=512)
+        check_status()
+        _check(acc - 1, ref, K)
+    check_status()
+    _check(out, ref, K)
 
 
 def test_strided_views_and_bn128():
