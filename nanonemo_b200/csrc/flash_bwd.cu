@@ -17,6 +17,7 @@
 // 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 compute: two threads per query row,
 // one for keys 0..63 of the tile and one for keys 64..127 (same TMEM lanes, different columns), which
 // halves the latency of the softmax phase the tensor core has to wait for. All waits are bounded.
+#include <cstdlib>
 #include <type_traits>
 
 #include "sm100.cuh"
@@ -350,6 +351,11 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
 
 }  // namespace
 
+int nnb_flash_bwd_t_impl(int hd, const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse, void* delta,
+                          void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, const long long* qs,
+                          const long long* ks, const long long* vs, const long long* os, const long long* dos, const long long* dqs,
+                          const long long* dks, const long long* dvs, float scale, void* status, cudaStream_t st);
+
 #ifdef NNB_PROFILE
 extern "C" int nnb_flash_bwd_prof_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_flash_prof, sizeof(g_flash_prof)); }
 #endif
@@ -364,9 +370,20 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
                              long long do_sb, long long do_st, long long do_sh, long long dq_sb, long long dq_st,
                              long long dq_sh, long long dk_sb, long long dk_st, long long dk_sh, long long dv_sb,
                              long long dv_st, long long dv_sh, float scale, int dtype, void* status, cudaStream_t st) {
-  NNB_REQUIRE(hd == HD, "flash_bwd: head_dim %d not supported (64)", hd);
+  NNB_REQUIRE(hd == HD || hd == 128, "flash_bwd: head_dim %d not supported (64, 128)", hd);
   NNB_REQUIRE(dtype == NNB_BF16, "flash_bwd: bf16 only");
   NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_bwd: bad shape");
+  // head_dim 128 runs on the transposed-tile kernel (flash_bwd_t.cu). It also serves head_dim 64
+  // (NANONEMO_FLASH_BWD=transposed), but there the 128 x 128 formulation of this file measured faster (0.43 vs 0.57 ms at
+  // B32 H12/4 T1024): with 64-wide tiles every MMA has N = 64 and is bound by shared-memory operand reads.
+  static const bool square = [] { const char* e = getenv("NANONEMO_FLASH_BWD"); return !(e && e[0] == 't'); }();
+  if (hd == 128 || !square) {
+    const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh}, os[3] = {o_sb, o_st, o_sh};
+    const long long dos[3] = {do_sb, do_st, do_sh}, dqs[3] = {dq_sb, dq_st, dq_sh}, dks[3] = {dk_sb, dk_st, dk_sh};
+    const long long dvs[3] = {dv_sb, dv_st, dv_sh};
+    return nnb_flash_bwd_t_impl(hd, q, k, v, o, d_o, lse, delta, dq_acc, dq, dk, dv, B, T, H, KVH, qs, ks, vs, os, dos, dqs, dks, dvs,
+                                scale, status, st);
+  }
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (!nnb_make_tmap_4d(&tq, dt, 2, q, hd, H, T, B, q_sh * 2, q_st * 2, q_sb * 2, 64, 1, BQ, "flash_bwd Q")) return -4;

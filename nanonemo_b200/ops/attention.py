@@ -99,7 +99,7 @@ class _FlashPacked(torch.autograd.Function):
         dq = dqkv[..., : H * hd].view(B, T, H, hd)
         dk = dqkv[..., H * hd:(H + KVH) * hd].view(B, T, KVH, hd)
         dv = dqkv[..., (H + KVH) * hd:].view(B, T, KVH, hd)
-        if _have_bwd() and hd == 64:
+        if _have_bwd() and hd in (64, 128):
             bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale)
         else:
             gq, gk, gv = _bwd_via_recompute(q, k, v, do)
@@ -135,7 +135,7 @@ class _Flash(torch.autograd.Function):
         B, T, H, hd = qt.shape
         dot = do.transpose(1, 2)
         dot = dot if dot.dtype == torch.bfloat16 and dot.stride(-1) == 1 else dot.to(torch.bfloat16).contiguous()
-        if _have_bwd() and hd == 64:
+        if _have_bwd() and hd in (64, 128):
             dq, dk, dv = torch.empty_like(o), torch.empty(kt.shape, dtype=o.dtype, device=o.device), torch.empty(vt.shape, dtype=o.dtype, device=o.device)
             bwd_raw(qt, kt, vt, o, lse, dot, dq, dk, dv, ctx.scale)
         else:

@@ -65,7 +65,9 @@ def test_packed_forward_and_backward():
     torch.testing.assert_close(qkv.grad.float(), ref_in.grad, rtol=5e-2, atol=5e-2)
 
 
-@pytest.mark.parametrize("B,H,KVH,T,hd", [(1, 2, 1, 256, 64), (2, 6, 2, 512, 64), (1, 3, 3, 200, 64), (1, 4, 2, 1024, 64)])
+@pytest.mark.parametrize("B,H,KVH,T,hd", [(1, 2, 1, 256, 64), (2, 6, 2, 512, 64), (1, 3, 3, 200, 64), (1, 4, 2, 1024, 64),
+                                          (1, 1, 1, 128, 128), (1, 2, 1, 256, 128), (2, 4, 2, 512, 128), (1, 3, 3, 200, 128),
+                                          (1, 4, 1, 1024, 128), (1, 2, 2, 37, 128)])
 def test_backward_matches_reference(B, H, KVH, T, hd):
     from nanonemo_b200 import ops
     from nanonemo_b200.ops.gemm import check_status
