@@ -109,6 +109,18 @@ class Attention(nn.Module):
                 y = self._attend(None, cos, sin, qkv=qkv, project=False)
                 return row_parallel_linear(y.reshape(-1, y.shape[-1]), self.wo.weight, ft)
             full = self.tp.gather_tokens(x).view(self.tp.B, self.tp.T, -1)
+            if self.tp.pair > 1:
+                # two ranks share this head group and split its query rows: the first attends over (and projects) the first
+                # half of every sequence, the second attends over the whole sequence and projects the second half; the rows
+                # a rank does not own enter the reduce-scatter as zeros
+                half = self.tp.T // 2
+                if self.tp.pair_pos == 0:
+                    mine = self._attend(full[:, :half], cos, sin)
+                    out = torch.cat((mine, mine.new_zeros(self.tp.B, self.tp.T - half, mine.shape[-1])), dim=1)
+                else:
+                    mine = self.wo(self._attend(full, cos, sin, project=False)[:, half:])
+                    out = torch.cat((mine.new_zeros(self.tp.B, half, mine.shape[-1]), mine), dim=1)
+                return self.tp.scatter_tokens(out.reshape(-1, x.shape[-1]))
             return self.tp.scatter_tokens(self._attend(full, cos, sin).reshape(-1, x.shape[-1]))
         return self._attend(x, cos, sin)
 

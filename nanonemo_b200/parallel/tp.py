@@ -14,7 +14,11 @@ the flattened (B*T) token axis, which makes every gather / scatter a contiguous 
 parameters live in a ``FlatParams`` store so clipping and AdamW are the fused flat kernels; and the
 operators on local tensors (norm, RoPE, attention, SwiGLU, GEMMs) are the same sm100 kernels as on
 one GPU — the reference has to force its ``torch`` norms and loss under TP (tp.py:37-38).
-With ``comm="fused"`` (and the sm100 GEMM) the four block linears run as single kernels that do the
+Degrees that do not divide the head counts (8 with 12 query / 4 KV heads) use rank PAIRS: the MLP, the vocabulary and the
+norms are split ``tp`` ways as usual, the heads ``tp / 2`` ways; the two ranks of a pair hold the same ``wqkv`` / ``wo``
+slices, attend over the first half (rank 0 of the pair) or the whole (rank 1) of every sequence and project only their own
+half of the query rows, contributing zeros for the other half to the reduce-scatter; their weight gradients are summed inside
+the pair. With ``comm="fused"`` (and the sm100 GEMM) the four block linears run as single kernels that do the
 collective themselves (parallel/tp_fused.py: all-gather -> GEMM and GEMM -> reduce-scatter over peer
 memory); the embedding / head / loss collectives and the CPU path use torch.distributed.
 """
@@ -33,6 +37,16 @@ class TPContext:
         self.fused_tp = fused_tp  # parallel.tp_fused.FusedTP: linears whose collective runs inside the GEMM kernel
         self.B = self.T = 0
         self.gloo = self.device.type != "cuda"
+        # attention layout (set_attention_layout): heads are split attn_world ways; when the heads do not divide by the
+        # degree, consecutive PAIRS of ranks share a head group (same wqkv / wo slices) and split its query rows
+        self.attn_world, self.attn_rank, self.pair, self.pair_pos, self.pair_group = world, rank, 1, 0, None
+
+    def set_attention_layout(self, cfg, pair_group=None):
+        self.attn_world, self.pair = attention_layout(cfg, self.world)
+        self.attn_rank, self.pair_pos = self.rank // self.pair, self.rank % self.pair
+        self.pair_group = pair_group
+        if self.pair > 1 and pair_group is None:
+            raise ValueError("a tensor-parallel degree that needs the pair split must be given the pair process group")
 
     # raw collectives on contiguous 2-D tensors, along dim 0
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
@@ -148,10 +162,20 @@ class _VocabParallelCE(torch.autograd.Function):
 
 
 # ----------------------------------------------------------------------------- model surgery
+def attention_layout(cfg, tp: int):
+    """(ways the heads are split, ranks per head group). Head-aligned when the degree divides both head counts (12 query /
+    4 KV heads: 1, 2, 4); otherwise pairs of ranks share a head group and split its query rows (12 / 4 heads at degree 8:
+    4 groups x 2) — the layout the reference refuses (nanonemo/distributed/tp.py:35-36)."""
+    if cfg.n_heads % tp == 0 and cfg.n_kv_heads % tp == 0:
+        return tp, 1
+    if tp % 2 == 0 and cfg.n_heads % (tp // 2) == 0 and cfg.n_kv_heads % (tp // 2) == 0:
+        return tp // 2, 2
+    raise ValueError(f"tensor parallel degree {tp} fits neither n_heads={cfg.n_heads} / n_kv_heads={cfg.n_kv_heads} "
+                     f"head-aligned nor with rank pairs sharing a head group")
+
+
 def check_divisible(cfg, tp: int):
-    if cfg.n_heads % tp or cfg.n_kv_heads % tp:
-        raise ValueError(f"tensor parallel degree {tp} must divide n_heads={cfg.n_heads} and n_kv_heads={cfg.n_kv_heads} "
-                         "(head-aligned split; 12 query / 4 KV heads allow tp in {1, 2, 4})")
+    attention_layout(cfg, tp)
     if cfg.d_ff % tp or cfg.vocab_size % tp:
         raise ValueError(f"tensor parallel degree {tp} must divide d_ff={cfg.d_ff} and vocab_size={cfg.vocab_size}")
 
@@ -161,14 +185,17 @@ def shard_model_(model, tp: TPContext):
     """Slice a fully initialised model in place to this rank's tensor-parallel shard."""
     cfg, r, W = model.cfg, tp.rank, tp.world
     check_divisible(cfg, W)
+    if (tp.attn_world, tp.pair) != attention_layout(cfg, W):
+        tp.set_attention_layout(cfg, tp.pair_group)
+    ar, aw = tp.attn_rank, tp.attn_world
     hd = cfg.head_dim
-    Hl, KVl, Fl, Vl = cfg.n_heads // W, cfg.n_kv_heads // W, cfg.d_ff // W, cfg.vocab_size // W
+    Hl, KVl, Fl, Vl = cfg.n_heads // aw, cfg.n_kv_heads // aw, cfg.d_ff // W, cfg.vocab_size // W
     for block in model.blocks:
         a, m = block.attn, block.mlp
         wq, wk, wv = a.split_qkv()
-        a.wqkv.weight.data = torch.cat((wq[r * Hl * hd:(r + 1) * Hl * hd], wk[r * KVl * hd:(r + 1) * KVl * hd],
-                                        wv[r * KVl * hd:(r + 1) * KVl * hd])).contiguous()
-        a.wo.weight.data = a.wo.weight[:, r * Hl * hd:(r + 1) * Hl * hd].contiguous()
+        a.wqkv.weight.data = torch.cat((wq[ar * Hl * hd:(ar + 1) * Hl * hd], wk[ar * KVl * hd:(ar + 1) * KVl * hd],
+                                        wv[ar * KVl * hd:(ar + 1) * KVl * hd])).contiguous()
+        a.wo.weight.data = a.wo.weight[:, ar * Hl * hd:(ar + 1) * Hl * hd].contiguous()
         a.n_heads, a.n_kv_heads, a.q_dim, a.kv_dim = Hl, KVl, Hl * hd, KVl * hd
         wg, wu = m.split_gu()
         m.w_gu.weight.data = torch.cat((wg[r * Fl:(r + 1) * Fl], wu[r * Fl:(r + 1) * Fl])).contiguous()
@@ -200,6 +227,8 @@ class TPStrategy(LocalStrategy):
         super().__init__(model, store, step_model)
         self.tp = tp
         self.replicated = [p for n, p in model.named_parameters() if shard_rule(n) is None]
+        # rank pairs that share a head group hold identical wqkv / wo slices, each with the gradient of its own query rows
+        self.duplicated = [p for n, p in model.named_parameters() if tp.pair > 1 and is_attention_weight(n)]
         self.dp_rank, self.dp_world = 0, 1  # every TP rank reads the same batch: one data-parallel replica
 
     def finish_grads(self):
@@ -212,11 +241,16 @@ class TPStrategy(LocalStrategy):
                 g = p._main_grad if hasattr(p, "_main_grad") else p.grad
                 g.copy_(flat[o:o + p.numel()].view(p.shape))
                 o += p.numel()
+        for p in self.duplicated:  # sum the two row halves' contributions: both ranks of a pair end with the same gradient
+            g = p._main_grad if hasattr(p, "_main_grad") else p.grad
+            dist.all_reduce(g, group=self.tp.pair_group)
 
     def global_sumsq(self):
         total = self.store.grad_sumsq()
-        rep = sum((p._main_grad.float().pow(2).sum() for p in self.replicated), torch.zeros((), device=total.device))
-        sharded = self.tp.all_reduce((total - rep).reshape(1).clone()).reshape(())
+        zero = torch.zeros((), device=total.device)
+        rep = sum((p._main_grad.float().pow(2).sum() for p in self.replicated), zero)
+        dup = sum((p._main_grad.float().pow(2).sum() for p in self.duplicated), zero)  # held by `pair` ranks: count once
+        sharded = self.tp.all_reduce((total - rep - dup + dup / self.tp.pair).reshape(1).clone()).reshape(())
         return sharded + rep
 
     # checkpoint state: gather the shards back to full tensors
@@ -244,6 +278,10 @@ class TPStrategy(LocalStrategy):
         super().load_from_checkpoint(opt, local)
 
 
+def is_attention_weight(name: str) -> bool:
+    return name.endswith("attn.wqkv.weight") or name.endswith("attn.wo.weight")
+
+
 def tp_full_tensor(name, local, tp, cfg):
     """All-gather a tensor-parallel shard of parameter `name` back to the full tensor."""
     rule = shard_rule(name)
@@ -252,6 +290,8 @@ def tp_full_tensor(name, local, tp, cfg):
     parts = [torch.empty_like(local) for _ in range(tp.world)]
     dist.all_gather(parts, local.detach().contiguous(), group=tp.group)
     hd, W = cfg.head_dim, tp.world
+    if is_attention_weight(name):
+        parts, W = parts[::tp.pair], tp.attn_world  # one copy per head group
     if rule == "qkv":
         q, kv = cfg.n_heads // W * hd, cfg.n_kv_heads // W * hd
         return torch.cat([p[:q] for p in parts] + [p[q:q + kv] for p in parts] + [p[q + kv:] for p in parts])
@@ -267,6 +307,8 @@ def tp_local_slice(name, full, tp, cfg):
     if rule is None:
         return full
     r, W, hd = tp.rank, tp.world, cfg.head_dim
+    if is_attention_weight(name):
+        r, W = tp.attn_rank, tp.attn_world
     if rule == "qkv":
         Q, KV = cfg.n_heads * hd, cfg.n_kv_heads * hd
         q, kv = Q // W, KV // W
@@ -278,10 +320,25 @@ def tp_local_slice(name, full, tp, cfg):
     return full.narrow(rule, r * n, n)
 
 
+def make_pair_group(tp_rank_lists, pair: int):
+    """Process groups of consecutive `pair` ranks inside every tensor-parallel group; every rank of the world creates every
+    group, in the same order, and gets back the one it belongs to."""
+    mine, me = None, dist.get_rank()
+    for ranks in tp_rank_lists:
+        for i in range(0, len(ranks), pair):
+            sub = ranks[i:i + pair]
+            grp = dist.new_group(sub)
+            if me in sub:
+                mine = grp
+    return mine
+
+
 def _maybe_fuse(tp, model_cfg, cfg, d, group):
     from nanonemo_b200.parallel.symm import fused_available
 
     tokens = cfg.micro_batch * cfg.seq_len
+    if tp.pair > 1:
+        return  # the pair split runs attention through the unfused gather / scatter path
     if (fused_available(d, cfg.comm) and model_cfg.resolved().linear_impl == "sm100" and cfg.precision in ("bf16", "fp16")
             and tokens % (128 * tp.world) == 0):
         from nanonemo_b200.parallel.tp_fused import FusedTP
@@ -302,6 +359,8 @@ def build_tp(model_cfg, cfg, d):
         if (cfg.tp_size or world) != world:
             raise ValueError("parallel=tp uses the whole world as the tensor-parallel group; use fsdp_tp for a 2-D mesh")
         tp = TPContext(dist.group.WORLD, rank, world, d.device)
+        _, pair = attention_layout(model_cfg, world)
+        tp.set_attention_layout(model_cfg, make_pair_group([list(range(world))], pair) if pair > 1 else None)
         model, step_model = build_model(model_cfg, cfg, d.device)
         shard_model_(model, tp)
         _maybe_fuse(tp, model_cfg, cfg, d, dist.group.WORLD)
@@ -323,6 +382,9 @@ def build_tp(model_cfg, cfg, d):
         if rank in ranks:
             dp_group = grp
     tp = TPContext(tp_group, rank % tps, tps, d.device)
+    if attention_layout(model_cfg, tps)[1] > 1:
+        raise ValueError(f"tp_size {tps} needs rank pairs to share a head group, which the 2-D fsdp_tp mesh does not support; "
+                         "use parallel=tp or a head-aligned tp_size")
     model, step_model = build_model(model_cfg, cfg, d.device)
     shard_model_(model, tp)
     _maybe_fuse(tp, model_cfg, cfg, d, tp_group)

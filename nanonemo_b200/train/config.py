@@ -123,17 +123,19 @@ def dump_config(model_cfg: ModelConfig, train_cfg: TrainConfig) -> str:
 
 def apply_overrides(model_cfg: ModelConfig, train_cfg: TrainConfig, overrides: list[str]):
     """``section.key=value`` overrides with YAML-parsed values (the CLIs' ``--set``)."""
+    updates = {"model": {}, "train": {}}
     for item in overrides:
-        target, _, raw = item.partition("=")
+        target, eq, raw = item.partition("=")
         section, _, key = target.partition(".")
-        if section not in ("model", "train") or not key or not _:
+        if section not in updates or not key or not eq:
             raise ValueError(f"bad override {item!r}: expected model.key=value or train.key=value")
         cfg = model_cfg if section == "model" else train_cfg
         if key not in {f.name for f in fields(cfg)}:
             raise ValueError(f"unknown {section} key {key!r}")
-        new = replace(cfg, **{key: yaml.safe_load(raw)})
-        if section == "model":
-            model_cfg = new
-        else:
-            train_cfg = new
+        updates[section][key] = yaml.safe_load(raw)
+    # one replace per section: keys that are only valid together (parallel=fsdp_tp + tp_size) may come in any order
+    if updates["model"]:
+        model_cfg = replace(model_cfg, **updates["model"])
+    if updates["train"]:
+        train_cfg = replace(train_cfg, **updates["train"])
     return model_cfg, train_cfg

@@ -111,3 +111,14 @@ def test_a_rank_that_never_joins_times_out_on_the_host(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
                         "127.0.0.1", "--master-port", "29547", str(script)], env=env, capture_output=True, text=True, timeout=120)
     assert "PEER LOST" in r.stdout + r.stderr, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+def test_tp_degree_beyond_the_kv_heads_uses_rank_pairs(tmp_path, single):
+    """4 tensor-parallel ranks with 2 KV heads: the heads split 2 ways, the ranks of a pair split the query rows (the layout
+    that serves TP=8 with 12 query / 4 KV heads). Losses must match one process, and the checkpoint — full tensors rebuilt
+    from one copy per head group — must resume in a single process."""
+    first, out = run(tmp_path, "pairs", 4, "train.parallel=tp", "train.max_steps=3", port=29547)
+    assert first == pytest.approx(single[:3], abs=1e-4)
+    (tmp_path / "b").mkdir()
+    rest, _ = run(tmp_path, "b", 1, "train.parallel=none", f"train.resume_from={out / 'ckpt'}")
+    assert first + rest == pytest.approx(single, abs=1e-4)
