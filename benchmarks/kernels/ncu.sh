@@ -5,7 +5,7 @@
 # The target runs once without the profiler first; the capture is 3 launches of one kernel and never
 # changes GPU clocks (--clock-control none).
 set -euo pipefail
-target=${1:?target: gemm|flash|rmsnorm|swiglu|rope|ce|adamw}
+target=${1:?target: gemm|gemm_single|gemm_mxfp8|flash|flash128|rmsnorm|swiglu|rope|ce|adamw}
 pattern=${2:?kernel name pattern, e.g. regex:gemm_tcgen05}
 out=${3:-gpurun_out}
 here=$(cd "$(dirname "$0")" && pwd)

@@ -1,7 +1,7 @@
 """Small profiler target: a few launches of one kernel family at a shape larger than L2 but holding only
 a few hundred MB, so an `ncu --set full` capture ends by itself in about a minute.
 
-    python benchmarks/kernels/ncu_target.py {gemm,flash,rmsnorm,swiglu,rope,ce,adamw} [iters]
+    python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,flash,flash128,rmsnorm,swiglu,rope,ce,adamw} [iters]
 """
 
 import sys
@@ -23,7 +23,21 @@ def main():
         from nanonemo_b200.ops.gemm import gemm
 
         a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(4096, 768, device=dev, dtype=bf)
-        fn = lambda: gemm(a, b)
+        fn = lambda: gemm(a, b)  # default dispatch: the CTA-pair kernel (gemm2_tcgen05_kernel)
+    elif kind == "gemm_single":
+        from nanonemo_b200.ops.gemm import gemm
+
+        a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(4096, 768, device=dev, dtype=bf)
+        fn = lambda: gemm(a, b, bn=256)
+    elif kind == "gemm_mxfp8":
+        from nanonemo_b200 import fp8
+
+        aq, asf, _, _ = fp8.quantize_mx(torch.randn(M, 768, device=dev, dtype=bf))
+        bq, bsf, _, _ = fp8.quantize_mx(torch.randn(4096, 768, device=dev, dtype=bf))
+        fn = lambda: fp8.gemm_mxfp8(aq, asf, bq, bsf)
+    elif kind == "flash128":
+        qkv = torch.randn(4, 2048, 24 * 128, device=dev, dtype=bf, requires_grad=True)
+        fn = lambda: ops.attention_packed(qkv, 16, 4, 128, impl="sm100").sum().backward()
     elif kind == "flash":
         qkv = torch.randn(8, 1024, 1280, device=dev, dtype=bf, requires_grad=True)
         fn = lambda: ops.attention_packed(qkv, 12, 4, 64, impl="sm100").sum().backward()

@@ -197,6 +197,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int key = kt * BKV + row;
     bool ok = true;
     constexpr float kLog2e = 1.4426950408889634f;
+    NNB_PROF_DECL;
     // dQ^T of visit m: TMEM (lane = head_dim index, columns = queries) -> fp32 staging [query][head_dim] -> TMA reduce-add
     auto drain_dq = [&](int m) -> bool {
       const int hq = kvh * p.group + m / n_qb, q0 = (first_qb + m % n_qb) * BQ;
@@ -204,6 +205,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       if (leader) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
       if (named_barrier_or(1, kComputeThreads, !ok)) return false;
+      NNB_PROF_ADD(2);
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_lane + C::kColdQ + half * 32, r);
       tmem_ld_wait();
@@ -222,6 +224,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_reduce_add_4d(&tmdQacc, s_base + C::kOffStage, 0, hq, q0, b);
         tma_commit_group();
       }
+      NNB_PROF_ADD(3);
       return true;
     };
     // L (log-sum-exp, log2 units) and D * scale of the 64 queries of a visit: threads 0..63 fetch L, 64..127 fetch D, one
@@ -235,6 +238,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     };
     float ld_next = fetch_ld(0);
     for (int n = 0; n < iters; ++n) {
+      NNB_PROF_T0;
       const int q0 = (first_qb + n % n_qb) * BQ;
       const int buf = n % NBUF;
       uint8_t* my_p = smem + C::kOffP + buf * kHalfK + row * 128;
@@ -248,6 +252,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (n >= NBUF && !mbar_wait(bar_pfree + 8 * buf, (n / NBUF - 1) & 1, abort_flag)) ok = false;
       if (named_barrier_or(1, kComputeThreads, !ok)) { ok = false; fail_role = 3; break; }  // L / D visible; all leave together
       tc_fence_after();
+      NNB_PROF_ADD(0);
       // per-element mask only on the diagonal blocks, at the end of the sequence or for padded key rows
       const bool need_mask = q0 < kt * BKV + BKV - 1 || q0 + BQ > p.T || kt * BKV + BKV > p.T;
       auto tile = [&](auto masked) {
@@ -287,6 +292,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar_pds + 8 * buf);
+      NNB_PROF_ADD(1);
       if (NBUF == 1) {
         // single score buffer: the next visit's math needs this visit's MMAs anyway, so drain dQ^T right away
         if (!drain_dq(n)) { ok = false; fail_role = 3; break; }
@@ -296,6 +302,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
     if (NBUF == 2 && ok && iters > 0 && !drain_dq(iters - 1)) { ok = false; fail_role = 3; }
+    NNB_PROF_FLUSH_N(iters);
     // dV then dK of this key tile: TMEM -> bf16 staging (the (Q | dO) ring: every load has been consumed) -> TMA store
     if (ok && iters > 0) {
       // bar_dq of the last visit was awaited in drain_dq, so every MMA (including the dV / dK accumulation) has completed
@@ -448,6 +455,10 @@ int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, con
 }
 
 }  // namespace
+
+#ifdef NNB_PROFILE
+extern "C" int nnb_flash_bwd_t_prof_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_flash_prof, sizeof(g_flash_prof)); }
+#endif
 
 // Same contract as nnb_flash_bwd (flash_bwd.cu), which forwards here. All tensors are [B, T, heads, hd] views given by
 // element strides {batch, t, head}; dq_acc: fp32 [B, T, H, hd] contiguous, ZERO on entry.
