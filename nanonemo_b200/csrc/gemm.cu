@@ -485,9 +485,10 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   const CUtensorMapDataType in_dt = dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const int sms = max_ctas > 0 ? min(max_ctas, nnb_num_sms()) : nnb_num_sms();
   // CTA-pair kernel (gemm2.cu): 256 x 256 tiles over two SMs. Measured faster than the single-CTA tiles at every shape of
-  // the 114M model (3-14 %), slower only for large cubes (8192^3), where the single-CTA raster does better.
+  // the 114M model (1-20 %: K = 768 with any N, or N = 768 with any K), slower when N and K are both large (the 1.3B
+  // shapes: 32768 x 2048 x 5632 runs at 1166 vs 1428 TFLOP/s; 8192^3 at 1233 vs 1274), where the single-CTA kernel stays.
   static const bool pair_enabled = [] { const char* e = getenv("NANONEMO_GEMM_PAIR"); return !(e && e[0] == '0'); }();
-  const bool big_cube = M >= 4096 && N >= 4096 && K >= 4096;
+  const bool big_cube = M >= 2048 && N >= 2048 && K >= 2048;
   if (mode == 0 && (bn_hint == 512 || (bn_hint == 0 && pair_enabled && M >= 256 && N >= 256 && !big_cube))) {
     const NnbGemm2Args g{A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, dtype, out_f32, accumulate, k_splits, max_ctas, status};
     const int rc = nnb_gemm2_launch(g, st);
