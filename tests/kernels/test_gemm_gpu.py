@@ -65,10 +65,11 @@ def test_wgrad_layout_fp32_out(M, N, K, k_splits):
 
 @pytest.mark.parametrize("layout", ["fprop", "dgrad", "wgrad"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 768), (1024, 2304, 768), (384, 1280, 1024), (2048, 256, 2048),
-                                   (304, 520, 136), (4096, 4352, 128)])
+                                   (304, 520, 136), (4096, 4352, 128), (21504, 256, 64), (32768, 768, 128), (21760, 520, 72)])
 def test_cta_pair_kernel(layout, M, N, K):
     """bn=512 selects the two-SM kernel (256 x 256 tiles, tcgen05.mma.cta_group::2); ragged edges and an odd number of
-    128-row blocks (the second CTA's last block lies outside the matrix) included."""
+    128-row blocks (the second CTA's last block lies outside the matrix) included; the three tall shapes leave a tail wave of
+    at most half the CTA pairs, which the kernel works on as 128-wide half tiles."""
     from nanonemo_b200.ops.gemm import check_status, gemm
 
     torch.manual_seed(M + N + K)
