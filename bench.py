@@ -72,9 +72,7 @@ def run_ours(a):
         raise SystemExit("the kernel library is not built: python -c 'import __graft_entry__ as g; g.build()'")
     model_cfg = ModelConfig.sm100() if a.kernels == "sm100" else ModelConfig(attn_backend="mem_efficient")
     par = a.parallel if world > 1 else "none"
-    if par == "tp":  # vocab-parallel embedding / loss run on the PyTorch operators; one replica = the whole group
-        model_cfg = ModelConfig.sm100(loss_kernel="torch", embed_kernel="torch") if a.kernels == "sm100" else model_cfg
-    dp = 1 if par == "tp" else world
+    dp = 1 if par == "tp" else world  # tensor parallel: one replica = the whole group
     cfg = TrainConfig(data_dir="synthetic", out_dir="runs/bench", seq_len=SEQ_LEN, micro_batch=a.micro_batch,
                       global_batch_tokens=a.micro_batch * SEQ_LEN * dp, total_tokens=10**12, precision="bf16",
                       parallel=par, ddp_bucket_mb=100.0, fsdp_prefetch=True, eval_every=10**9)

@@ -43,7 +43,8 @@ def run(tmp_path, name, nproc, *overrides, loss="sm100", embed="sm100", port=295
     ("fsdp", ("train.comm=nccl",), "sm100", "sm100"),
     ("tp", ("train.comm=nccl",), "torch", "torch"),
     ("tp", ("train.comm=fused",), "torch", "torch"),
-], ids=["ddp_fused", "ddp_nccl", "fsdp_fused", "fsdp_nccl", "tp_nccl", "tp_fused"])
+    ("tp", ("train.comm=fused",), "sm100", "sm100"),  # vocabulary-parallel fused linear + cross-entropy kernels
+], ids=["ddp_fused", "ddp_nccl", "fsdp_fused", "fsdp_nccl", "tp_nccl", "tp_fused", "tp_fused_loss"])
 def test_two_gpus_track_one_gpu(tmp_path, par, extra, loss, embed):
     single = run(tmp_path, "one", 1, "train.parallel=none", loss=loss, embed=embed)
     multi = run(tmp_path, "two", 2, f"train.parallel={par}", *extra, loss=loss, embed=embed)
