@@ -122,3 +122,36 @@ def test_tp_degree_beyond_the_kv_heads_uses_rank_pairs(tmp_path, single):
     (tmp_path / "b").mkdir()
     rest, _ = run(tmp_path, "b", 1, "train.parallel=none", f"train.resume_from={out / 'ckpt'}")
     assert first + rest == pytest.approx(single, abs=1e-4)
+
+
+def test_attention_layout_and_pair_slices_without_processes():
+    """Pure layout logic: which degrees are head-aligned, which use rank pairs, and that the pair layout's local slices are
+    identical inside a pair and rebuild the full tensors when one copy per head group is concatenated."""
+    import types
+
+    import torch
+
+    from nanonemo_b200.models.config import ModelConfig
+    from nanonemo_b200.parallel.tp import attention_layout, tp_local_slice
+
+    cfg = ModelConfig()  # 12 query / 4 KV heads
+    assert [attention_layout(cfg, t) for t in (1, 2, 4, 8)] == [(1, 1), (2, 1), (4, 1), (4, 2)]
+    with pytest.raises(ValueError):
+        attention_layout(cfg, 3)
+    with pytest.raises(ValueError):
+        attention_layout(cfg, 16)
+    hd, D = cfg.head_dim, cfg.d_model
+    full_qkv = torch.arange((cfg.n_heads + 2 * cfg.n_kv_heads) * hd * 4, dtype=torch.float32).view(-1, 4)
+    full_wo = torch.arange(D * cfg.n_heads * hd, dtype=torch.float32).view(D, cfg.n_heads * hd)
+    ranks = [types.SimpleNamespace(rank=r, world=8, attn_rank=r // 2, attn_world=4, pair=2) for r in range(8)]
+    qkv = [tp_local_slice("blocks.0.attn.wqkv.weight", full_qkv, tp, cfg) for tp in ranks]
+    wo = [tp_local_slice("blocks.0.attn.wo.weight", full_wo, tp, cfg) for tp in ranks]
+    for p in range(4):
+        assert torch.equal(qkv[2 * p], qkv[2 * p + 1]) and torch.equal(wo[2 * p], wo[2 * p + 1])
+    q, kv = cfg.n_heads // 4 * hd, cfg.n_kv_heads // 4 * hd
+    parts = qkv[::2]
+    rebuilt = torch.cat([x[:q] for x in parts] + [x[q:q + kv] for x in parts] + [x[q + kv:] for x in parts])
+    assert torch.equal(rebuilt, full_qkv) and torch.equal(torch.cat(wo[::2], dim=1), full_wo)
+    # the MLP stays split 8 ways
+    full_down = torch.arange(D * cfg.d_ff, dtype=torch.float32).view(D, cfg.d_ff)
+    assert tp_local_slice("blocks.0.mlp.w_down.weight", full_down, ranks[3], cfg).shape == (D, cfg.d_ff // 8)
