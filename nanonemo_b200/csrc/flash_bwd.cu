@@ -305,9 +305,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; 8 lanes per (b, t, h) row of 64 elements,
-// 16 bytes per lane per tensor.
+// 16 bytes per lane per tensor. The same pass clears the fp32 dQ accumulator (its rows are visited in the same order).
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                   float* __restrict__ delta, int B, int T, int H, long long o_sb, long long o_st,
+                                   float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H, long long o_sb, long long o_st,
                                    long long o_sh, long long do_sb, long long do_st, long long do_sh) {
   const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long w = gid >> 3;
@@ -325,6 +325,9 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
     Chunk8<__nv_bfloat16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
 #pragma unroll
     for (int i = 0; i < 8; ++i) s += a[i] * g[i];
+    float4* z = reinterpret_cast<float4*>(dq_acc + w * HD + sub * 8);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   s += __shfl_xor_sync(0xffffffffu, s, 4);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -362,7 +365,7 @@ extern "C" int nnb_flash_bwd_prof_read(unsigned long long* out) { return (int)cu
 
 // All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16.
 // lse: fp32 [B, H, T] from the forward pass; delta: fp32 [B, H, T] scratch (written here);
-// dq_acc: fp32 [B, T, H, 64] contiguous, ZERO on entry (partial tiles are reduce-added into it).
+// dq_acc: fp32 [B, T, H, hd] contiguous scratch (cleared by the delta pre-pass; partial tiles are reduce-added into it).
 extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
                              void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, int hd,
                              long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st, long long k_sh,
@@ -397,7 +400,7 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
 
   const long long rows = (long long)B * T * H;
   flash_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
-                                                                          (float*)delta, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
+                                                                          (float*)delta, (float*)dq_acc, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
   NNB_LAUNCH_OK("flash_delta");
 
   BParams p{};

@@ -358,10 +358,11 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; HD / 8 lanes per row, 16 bytes per lane per tensor.
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; HD / 8 lanes per row, 16 bytes per lane per tensor. The same pass
+// clears the fp32 dQ accumulator (its rows are visited in the same order).
 template <int HD>
 __global__ void flash_delta_t_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                     float* __restrict__ delta, int B, int T, int H, long long o_sb, long long o_st,
+                                     float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H, long long o_sb, long long o_st,
                                      long long o_sh, long long do_sb, long long do_st, long long do_sh) {
   constexpr int L = HD / 8;
   const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -380,6 +381,9 @@ __global__ void flash_delta_t_kernel(const __nv_bfloat16* __restrict__ o, const 
     Chunk8<__nv_bfloat16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
 #pragma unroll
     for (int i = 0; i < 8; ++i) s += a[i] * g[i];
+    float4* z = reinterpret_cast<float4*>(dq_acc + w * HD + sub * 8);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 #pragma unroll
   for (int o2 = L / 2; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
@@ -423,7 +427,7 @@ int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, con
 
   const long long rows = (long long)B * T * H;
   flash_delta_t_kernel<HD><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, (float*)delta, B, T, H, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, (float*)delta, (float*)dq_acc, B, T, H, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
   NNB_LAUNCH_OK("flash_delta");
   BParams p{};
   p.B = B; p.H = H; p.KVH = KVH; p.T = T;
@@ -461,7 +465,7 @@ extern "C" int nnb_flash_bwd_t_prof_read(unsigned long long* out) { return (int)
 #endif
 
 // Same contract as nnb_flash_bwd (flash_bwd.cu), which forwards here. All tensors are [B, T, heads, hd] views given by
-// element strides {batch, t, head}; dq_acc: fp32 [B, T, H, hd] contiguous, ZERO on entry.
+// element strides {batch, t, head}; dq_acc: fp32 [B, T, H, hd] contiguous scratch (cleared by the delta pre-pass).
 int nnb_flash_bwd_t_impl(int hd, const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
                          void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, const long long* qs,
                          const long long* ks, const long long* vs, const long long* os, const long long* dos, const long long* dqs,

@@ -41,7 +41,7 @@ def bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale):
     KVH = k.shape[2]
     # delta = rowsum(dO * O) is computed inside the launcher's pre-pass kernel
     delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
-    dq_acc = torch.zeros((B, T, H, hd), dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty((B, T, H, hd), dtype=torch.float32, device=q.device)  # cleared by the kernel's pre-pass
     _lib.call("nnb_flash_bwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
               _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.i32(B), _lib.i32(T),
               _lib.i32(H), _lib.i32(KVH), _lib.i32(hd), *(_lib.i64(s) for s in _strides_bthd(q)),

@@ -1,0 +1,27 @@
+"""scripts/make_figures.py builds its tables from results/ JSON only (nothing is measured); works without matplotlib."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+
+
+def test_tables_from_results_only(tmp_path):
+    ladder = tmp_path / "results" / "ladder" / "b200"
+    ladder.mkdir(parents=True)
+    for i, name in enumerate(("s0_fp32", "s1_fp16")):
+        (ladder / f"{name}.json").write_text(json.dumps({"tokens_per_s": {"median": 1000.0 * (i + 1)}, "step_ms": {"median": 16.0 / (i + 1)}}))
+    dist = tmp_path / "results" / "dist" / "b200-x2"
+    dist.mkdir(parents=True)
+    (dist / "ddp.json").write_text(json.dumps({"tokens_per_s": {"median": 5000.0}, "bench": {"world": 2}}))
+    kern = tmp_path / "results" / "kernels"
+    kern.mkdir(parents=True)
+    (kern / "gemm.json").write_text(json.dumps({"device": "B200", "rows": [{"shape": "qkv", "ours_ms": 0.1}]}))
+    out = tmp_path / "figures"
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "make_figures.py"), "--results", str(tmp_path / "results"), "--out", str(out)],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    text = (out / "tables.md").read_text()
+    assert "| b200 | s0_fp32 | 1,000 | 16.00 |" in text and "| b200-x2 | ddp | 5,000 | 2 |" in text and "| qkv | 0.1 |" in text
