@@ -28,6 +28,7 @@ from nanonemo_b200.parallel.strategy import LocalStrategy
 from nanonemo_b200.train import checkpoint
 from nanonemo_b200.train.config import TrainConfig, dump_config
 from nanonemo_b200.train.optim import build_optimizer, lr_at
+from nanonemo_b200.utils import nvtx
 from nanonemo_b200.utils.env import git_info
 from nanonemo_b200.utils.mfu import flops_per_token, mfu, peak_tflops
 
@@ -156,13 +157,15 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
             loss_sum = loss.clone() if loss_sum is None else loss_sum + loss
             continue
         with strategy.sync_ctx(i == accum - 1), strategy.loss_ctx():
-            with torch.autocast(x.device.type, dtype=amp_dtype, enabled=amp_dtype is not None), strategy.fwd_ctx():
+            with nvtx.span("forward"), torch.autocast(x.device.type, dtype=amp_dtype, enabled=amp_dtype is not None), strategy.fwd_ctx():
                 _, loss = model(x, y)
             loss = loss / accum  # the summed .grad is then the gradient of the mean loss
-            (scaler.scale(loss) if scaler else loss).backward()
+            with nvtx.span("backward"):
+                (scaler.scale(loss) if scaler else loss).backward()
         loss = strategy.full_loss(loss.detach())
         loss_sum = loss if loss_sum is None else loss_sum + loss
-    grad_norm = strategy.step(opt, grad_clip, scaler, keep_grads)
+    with nvtx.span("optimizer"):
+        grad_norm = strategy.step(opt, grad_clip, scaler, keep_grads)
     both = torch.stack((parallel.all_mean(loss_sum.float()).reshape(()), grad_norm.float().reshape(())))
     if not host_sync:
         return both

@@ -25,3 +25,13 @@ def test_tables_from_results_only(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     text = (out / "tables.md").read_text()
     assert "| b200 | s0_fp32 | 1,000 | 16.00 |" in text and "| b200-x2 | ddp | 5,000 | 2 |" in text and "| qkv | 0.1 |" in text
+
+
+def test_nvtx_spans_are_noops_without_cuda(monkeypatch):
+    from nanonemo_b200.utils import nvtx
+
+    monkeypatch.setattr(nvtx, "_ON", None)
+    monkeypatch.setenv("NANONEMO_NVTX", "1")
+    with nvtx.span("forward"):
+        x = 1 + 1
+    assert x == 2
