@@ -31,7 +31,7 @@ def assert_guards_intact(big, view, pad_rows=3, pad_cols=8):
 
 
 @pytest.mark.parametrize("bn", [0, 256, 128, 512])
-@pytest.mark.parametrize("M,N,K", [(300, 520, 136), (128, 128, 64), (1000, 776, 264), (2560, 264, 72)])
+@pytest.mark.parametrize("M,N,K", [(304, 520, 136), (128, 128, 64), (1000, 776, 264), (2560, 264, 72)])
 def test_gemm_writes_its_output_and_nothing_else(M, N, K, bn):
     from nanonemo_b200.ops.gemm import check_status, gemm
 
