@@ -8,10 +8,13 @@
 //   warp 1        MMA issuer: S_j = Q K_j^T and O_j = P_j V_j with tcgen05.mma, accumulators in TMEM;
 //   warps 2..5    softmax, one thread per query row (= TMEM lane): tcgen05.ld the scores, online max and
 //                 sum with exp2, bf16 P_j into a 128-byte swizzled shared tile (the A operand of the second
-//                 MMA), and the partial O_j folded from TMEM into fp32 register accumulators.
-// The score tile, the P tile and (at head_dim 64) the partial-O tile are DOUBLE BUFFERED and the MMA warp
-// runs two tiles ahead: S_{j+2} is issued as soon as the softmax threads have read S_j, and P_j V_j runs
-// while they work on tile j+1, so neither side waits for a hand-off in steady state.
+//                 MMA). O accumulates IN TENSOR MEMORY over the key tiles; the row maximum used for the
+//                 exponentials is only raised when a tile exceeds it by more than 2^8 (probabilities then
+//                 stay below 256, exact in fp32 / safe in bf16), so the accumulator has to be rescaled —
+//                 tcgen05.ld, multiply, tcgen05.st by the softmax threads — on a few tiles only.
+// The score tile and the P tile are DOUBLE BUFFERED and the MMA warp runs two tiles ahead: S_{j+2} is
+// issued as soon as the softmax threads have read S_j, and P_j V_j runs while they work on tile j+1, so
+// neither side waits for a hand-off in steady state.
 // Outputs: O (bf16) through a swizzled staging tile + TMA store, and L = m * scale + ln(l) per row (fp32)
 // for the backward pass. Every mbarrier wait is bounded; on expiry the kernel records a status word
 // and leaves cleanly.
@@ -39,7 +42,6 @@ template <int HD>
 struct FCfg {
   static constexpr int BN = 64;                             // keys per KV tile
   static constexpr int kStages = 3;  // 3 x 16 KB at head_dim 64: two CTAs (2 x ~100 KB) fit in one SM
-  static constexpr int kOBufs = (HD == 64) ? 2 : 1;         // partial-O buffers in TMEM
   static constexpr int kCtasPerSm = (HD == 64) ? 2 : 1;
   static constexpr int kQBytes = BQ * HD * 2;               // HD/64 swizzled K-blocks of 16 KB
   static constexpr int kKBytes = BN * HD * 2;
@@ -47,8 +49,8 @@ struct FCfg {
   static constexpr int kPBytes = BQ * BN * 2;               // one swizzled K-block of 16 KB per buffer
   static constexpr int kSmem = kQBytes + kStages * (kKBytes + kVBytes) + 2 * kPBytes + 1024 + 256;
   static constexpr int kColS = 0;                           // S buffers at columns 0 and 64
-  static constexpr int kColO = 128;                         // partial-O buffers from column 128
-  static constexpr int kTmemCols = (128 + kOBufs * HD) <= 256 ? 256 : 512;
+  static constexpr int kColO = 128;                         // O accumulator from column 128
+  static constexpr int kTmemCols = 256;
 };
 
 struct FParams {
@@ -73,10 +75,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sKV = sQ + C::kQBytes;                              // [stages][K | V]
   uint8_t* sP = sKV + C::kStages * (C::kKBytes + C::kVBytes);  // [2][kPBytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::kPBytes);
-  // barriers: q_full, k_full[S], v_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_free[2]
+  // barriers: q_full, k_full[S], v_full[S], kv_empty[S], s_full[2], p_full[2], o_tile, o_all (+ 2 unused slots)
   const uint32_t bar_q = smem_u32(bars);
   const uint32_t bar_k = bar_q + 8, bar_v = bar_k + 8 * C::kStages, bar_e = bar_v + 8 * C::kStages;
-  const uint32_t bar_s = bar_e + 8 * C::kStages, bar_p = bar_s + 16, bar_o = bar_p + 16, bar_of = bar_o + 16;
+  const uint32_t bar_s = bar_e + 8 * C::kStages, bar_p = bar_s + 16, bar_o = bar_p + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 3 * C::kStages + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -98,7 +100,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar_s + 8 * i, 1);
       mbar_init(bar_p + 8 * i, kSoftmaxThreads);
       mbar_init(bar_o + 8 * i, 1);
-      mbar_init(bar_of + 8 * i, kSoftmaxThreads);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -160,18 +161,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (ok && n_kv > 1) ok = issue_s(1);
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t s = j % C::kStages, ph = (j / C::kStages) & 1;
-        const int pb = j & 1, ob = j % C::kOBufs;
+        const int pb = j & 1;
         if (!mbar_wait(bar_v + 8 * s, ph, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(bar_p + 8 * pb, (j >> 1) & 1, abort_flag)) { ok = false; break; }   // P_j written, S_j consumed
-        if (j >= C::kOBufs && !mbar_wait(bar_of + 8 * ob, ((j / C::kOBufs) - 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_p + 8 * pb, (j >> 1) & 1, abort_flag)) { ok = false; break; }   // P_j written, S_j consumed, O rescaled if needed
         tc_fence_after();
         const uint32_t sv = smem_u32(sKV) + s * (C::kKBytes + C::kVBytes) + C::kKBytes;
         const uint32_t sp = smem_u32(sP) + pb * C::kPBytes;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)  // P is K-major over keys; V is MN-major: 16 key rows (2048 B) per step
-          umma_f16(tmem_base + C::kColO + ob * HD, make_smem_desc(sp + k * 32, 16, 1024),
-                   make_smem_desc(sv + k * (16 * 128), BN * 128, 1024), p.idesc_pv, k > 0 ? 1u : 0u);
-        umma_commit(bar_o + 8 * ob);
+          umma_f16(tmem_base + C::kColO, make_smem_desc(sp + k * 32, 16, 1024),
+                   make_smem_desc(sv + k * (16 * 128), BN * 128, 1024), p.idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_o);  // one completion per tile: O holds the sum over tiles 0..j
+        if (j == n_kv - 1) umma_commit(bar_o + 8);  // one-shot "all products done" for the epilogue (no phase aliasing)
         umma_commit(bar_e + 8 * s);  // K_j and V_j are free once everything issued so far has run
         if (j + 2 < n_kv) ok = issue_s(j + 2);  // score buffer j & 1 was released by bar_p above
       }
