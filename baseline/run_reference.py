@@ -72,7 +72,7 @@ def _write_dataset(root: Path, train_tokens: int, val_tokens: int, seed: int = 0
 
 def main(a):
     if not (REF / "nanonemo").is_dir():
-        return unavailable("baseline/_ref is empty: install with pip --no-index --no-deps --target baseline/_ref /root/reference")
+        return unavailable("baseline/_ref is empty: install the reference package with pip --no-index --no-deps --target baseline/_ref <reference checkout>")
     import torch
 
     if not torch.cuda.is_available():

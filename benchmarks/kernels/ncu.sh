@@ -7,7 +7,7 @@
 set -euo pipefail
 target=${1:?target: gemm|gemm_single|gemm_mxfp8|flash|flash128|rmsnorm|swiglu|rope|ce|adamw}
 pattern=${2:?kernel name pattern, e.g. regex:gemm_tcgen05}
-out=${3:-gpurun_out}
+out=${3:-ncu_out}
 here=$(cd "$(dirname "$0")" && pwd)
 mkdir -p "$out"
 python "$here/ncu_target.py" "$target" 4 > "$out/${target}_plain.log" 2>&1 &&

@@ -3,7 +3,7 @@
 list of the profiling recipe, or `nsys stats --report cuda_gpu_kern_sum --format csv`). Communication =
 NCCL kernels plus this framework's collective kernels (allreduce_f32 / reduce_scatter_f32 / allgather).
 
-    python scripts/comm_share.py gpurun_out/launches.csv
+    python scripts/comm_share.py launches.csv
 """
 
 import csv
