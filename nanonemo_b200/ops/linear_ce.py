@@ -38,7 +38,7 @@ def linear_ce_fwd(x16, w16, targets, chunk_rows, dW_out):
         xc = x16[r0:r1]
         gemm(xc, w16, out=lg)
         ce_inplace(lg, targets[r0:r1], loss_rows[r0:r1], 1.0 / N)
-        gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=256 if r1 - r0 >= 16384 else 128)
+        gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=0 if r1 - r0 >= 16384 else 128)
         gemm(lg, xc, a_mn=True, b_mn=True, out=dW_out, accumulate=True)
     return loss_rows.sum(), dx
 
@@ -126,7 +126,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
             lg, xc = logits[: r1 - r0], x16[r0:r1]
             gemm(xc, w16, out=lg)
             vocab_parallel_ce_inplace(lg, tg[r0:r1], loss_rows[r0:r1], 1.0 / N, v0, Vl * tp.world, tp.all_gather, tp.world)
-            gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=256 if r1 - r0 >= 16384 else 128)
+            gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=0 if r1 - r0 >= 16384 else 128)
             gemm(lg, xc, a_mn=True, b_mn=True, out=dW, accumulate=True)
         ctx.save_for_backward(dx, dW, weight)
         ctx.x_dtype = x.dtype
