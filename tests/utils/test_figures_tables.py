@@ -35,3 +35,17 @@ def test_nvtx_spans_are_noops_without_cuda(monkeypatch):
     with nvtx.span("forward"):
         x = 1 + 1
     assert x == 2
+
+
+def test_step_breakdown_groups_kernel_names():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("step_breakdown", ROOT / "scripts" / "step_breakdown.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.group_of("(anonymous namespace)::gemm2_tcgen05_kernel(CUtensorMap_st)") == "tcgen05 GEMM (CTA pair)"
+    assert mod.group_of("void (anonymous namespace)::gemm_tcgen05_kernel<256, false>(...)") == "tcgen05 GEMM (single CTA)"
+    assert mod.group_of("(anonymous namespace)::flash_delta_kernel(...)") == "flash attention backward"
+    assert mod.group_of("void add_rmsnorm_bwd_kernel<float, __nv_bfloat16, __nv_bfloat16, 3>") == "add + RMSNorm"
+    assert mod.group_of("ncclDevKernel_AllReduce_Sum_f32_RING_LL") == "collectives"
+    assert mod.group_of("something_else") == "other"
