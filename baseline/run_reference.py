@@ -70,7 +70,7 @@ def _write_dataset(root: Path, train_tokens: int, val_tokens: int, seed: int = 0
     (root / "manifest.json").write_text(json.dumps({"tokenizer": "gpt2", "splits": splits}))
 
 
-def main(a):
+def main(a, headline_config=None):
     if not (REF / "nanonemo").is_dir():
         return unavailable("baseline/_ref is empty: install the reference package with pip --no-index --no-deps --target baseline/_ref <reference checkout>")
     import torch
@@ -126,11 +126,9 @@ def main(a):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random token ids in [0, 50257) in the reference shard format; random-init weights",
             "impl": "reference",
-            "config": {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)", "global_batch": micro * dp,
-                       "seq_len": seq, "micro_batch_per_gpu": micro,
-                       "parallelism": {"ddp": f"dp{world}", "none": "dp1", "fsdp": f"fsdp{world}", "tp": f"tp{world}+sp"}[par],
-                       "stack": "torch.compile default + mem_efficient SDPA + torch DDP/NCCL + foreach AdamW",
-                       "l2": "no flush: per-step working set is far larger than the 126 MB L2"},
+            "config": headline_config(micro, seq, world, par) if headline_config else {"global_batch": micro * dp, "seq_len": seq},
+            "stack": "torch.compile default + mem_efficient SDPA + torch DDP/NCCL + foreach AdamW",
+            "comparable": "e2e.value (both arms time their public train_step with the host copies inside the region)",
             # The reference's benchmark() times its real train_step: every step includes the pinned
             # H2D copy of the batch and the .item() reads of loss and grad norm, so its device-timed
             # number already is its end-to-end number.

@@ -33,6 +33,25 @@ BASELINE_TOKENS_PER_S = None  # the reference publishes no B200 number (BASELINE
 MICRO_BATCH, SEQ_LEN = 32, 1024
 
 
+def headline_config(micro_batch: int, seq_len: int, world: int, parallel: str) -> dict:
+    """The `config` entry of the JSON line: the same keys and values for both arms (what differs between the arms is the
+    implementation, printed under `stack`)."""
+    dp = 1 if parallel == "tp" else world
+    return {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)", "global_batch": micro_batch * dp,
+            "seq_len": seq_len, "micro_batch_per_gpu": micro_batch,
+            "parallelism": {"ddp": f"dp{world}", "none": "dp1", "fsdp": f"fsdp{world}", "tp": f"tp{world}+sp"}[parallel],
+            "optimizer": "AdamW + clip 1.0, fp32 master weights",
+            "l2": "no flush: per-step working set (0.46 GB weights + ~10 GB activations) is far larger than the 126 MB L2"}
+
+
+def measured_peaks() -> dict:
+    """bf16 GEMM throughput measured on this pool's B200 by the driver (burst and sustained TFLOP/s), if the file is there."""
+    try:
+        return json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except (OSError, ValueError):
+        return {}
+
+
 def parse():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -106,7 +125,13 @@ def run_ours(a):
     # End-to-end mode reads every step's (loss, grad norm) back to the host, but one step late: the device -> host copy of
     # step i is enqueued behind step i and collected after step i + 1 has been launched, so the GPU never waits for the host
     # (the usual way a training loop logs its loss). Each step still does its own pinned host -> device copy of the batch.
-    slots = [(torch.empty(2, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+    slots = [(torch.empty(3, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+
+    def collect(buf):
+        vals = buf.tolist()
+        if vals[2] != 0:  # a bounded wait inside a kernel ran out: the step's work was skipped, the number would be a lie
+            strategy.raise_on_status()
+        return vals
 
     def timed(src, host_sync):
         fence()
@@ -124,11 +149,11 @@ def run_ours(a):
             ev.record()
             if pending is not None:
                 pending[1].synchronize()
-                last = pending[0].tolist()
+                last = collect(pending[0])
             pending = (buf, ev)
         if pending is not None:
             pending[1].synchronize()
-            last = pending[0].tolist()
+            last = collect(pending[0])
         e1.record()
         fence()
         ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=d.device)
@@ -146,6 +171,9 @@ def run_ours(a):
         launches0 = _lib.LAUNCHES + strategy.launches
         ms_dev, win_dev, last = timed(staged, False)
         launches = _lib.LAUNCHES + strategy.launches - launches0
+        last = last.tolist()
+        if len(last) > 2 and last[2] != 0:
+            strategy.raise_on_status()
         loss_dev = float(last[0])
         time.sleep(0.25)  # let the sampler flush the last lines of the window
     finally:
@@ -156,6 +184,7 @@ def run_ours(a):
     samples = mon.window(*win_dev) or mon.window(win_e2e[0], win_dev[1])  # a very short device-timed region may fall between two samples
     clocks = clocks_record(samples)
     flops_tok = flops_per_token(model_cfg, cfg.seq_len)
+    peaks = measured_peaks()
     if d.main:
         print(json.dumps({
             "metric": "train tokens/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
@@ -164,14 +193,18 @@ def run_ours(a):
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16", "data": "synthetic uniform-random token ids in [0, 50257); random-init weights",
             "impl": "ours", "kernels": a.kernels,
-            "config": {"model": "NanoNemo-114M (12L, d768, 12Q/4KV, ff2048, vocab 50304)",
-                       "global_batch": cfg.micro_batch * dp, "seq_len": cfg.seq_len, "micro_batch_per_gpu": cfg.micro_batch,
-                       "parallelism": {"ddp": f"dp{world}", "none": "dp1", "fsdp": f"fsdp{world}", "tp": f"tp{world}+sp"}[par], "optimizer": "AdamW + clip 1.0, fp32 master weights",
-                       "l2": "no flush: per-step working set (0.46 GB weights + ~10 GB activations) is far larger than the 126 MB L2"},
+            "config": headline_config(cfg.micro_batch, cfg.seq_len, world, par),
+            "stack": "tcgen05 GEMMs with fused RoPE / SwiGLU / softmax-statistics epilogues, tcgen05 FlashAttention, fused norms, "
+                     "peer-memory collective kernels on a side stream, one-kernel clip + AdamW"
+                     + (", micro-batch replayed from a CUDA graph" if getattr(strategy, "use_cuda_graph", False) else ""),
             "mfu_vs_nominal_2250": value / world * flops_tok / 2250e12,
+            "mfu_vs_measured_burst": (value / world * flops_tok / (peaks["bf16_tflops"] * 1e12)) if peaks.get("bf16_tflops") else None,
+            "mfu_vs_measured_sustained": (value / world * flops_tok / (peaks["bf16_tflops_sustained"] * 1e12))
+            if peaks.get("bf16_tflops_sustained") else None,
+            "comparable": "e2e.value (both arms time their public train_step with the host copies inside the region)",
             "loss_last": loss_dev,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
-                    "h2d_bytes_per_step": loader.h2d_bytes_per_batch * accum, "d2h_bytes_per_step": 8,
+                    "h2d_bytes_per_step": loader.h2d_bytes_per_batch * accum, "d2h_bytes_per_step": 12,
                     "loss_last": last_e2e[0], "result_read": "every step, collected one step late (non-blocking copy + event)"},
             "gpu_launches": launches,
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
@@ -185,7 +218,7 @@ def main():
     if a.impl == "reference":
         from baseline.run_reference import main as ref_main
 
-        return ref_main(a)
+        return ref_main(a, headline_config)
     return run_ours(a)
 
 

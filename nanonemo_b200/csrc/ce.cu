@@ -103,8 +103,10 @@ __device__ __forceinline__ void row_write_grad(T* __restrict__ x, int nvec, long
   }
 }
 
-// One block per row, two sweeps. Sweep 1 reads the row from HBM; sweep 2 re-reads it — a row is ~100 KB and a few hundred
-// rows are in flight, far below the 126 MB L2, so the second read does not reach HBM — and overwrites it with the gradient.
+// One block per row, two sweeps. Sweep 1 reads the row from HBM; sweep 2 re-reads it and overwrites it with the gradient.
+// A row is ~100 KB and a few hundred rows are in flight, so the re-read is meant to hit L2; measured, about half of it still
+// reaches HBM (the GEMM that wrote the logits and the gradient writes compete for the same L2), which is why the fused
+// head uses ce_grad_from_stats_kernel (one sweep) whenever the GEMM epilogue could produce the statistics.
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
                                                                 float* __restrict__ loss_rows, int V, long long ld,
@@ -121,6 +123,50 @@ __global__ void __launch_bounds__(kCeThreads) ce_inplace_kernel(T* __restrict__ 
   const float lse = ms.x + logf(ms.y);
   if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
   row_write_grad<T>(x, V >> 3, tgt, lse, valid ? grad_scale : 0.f);  // ignored rows contribute no gradient
+}
+
+// One-sweep form: the head GEMM's epilogue already reduced every 256-column tile of the row to (max, sum of exp(x - max))
+// (`tile_stats` [R, n_tiles, 2], written by nnb_gemm_ce_stats); the block combines the n_tiles pairs, writes the row loss and
+// overwrites the row with the gradient. The logits are read once and written once.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads) ce_grad_from_stats_kernel(T* __restrict__ logits, const long long* __restrict__ targets,
+                                                                        const float* __restrict__ tile_stats, int n_tiles,
+                                                                        float* __restrict__ loss_rows, int V, long long ld,
+                                                                        float grad_scale) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  __shared__ float s_m[kCeThreads / 32], s_s[kCeThreads / 32];
+  const long long row = blockIdx.x;
+  T* x = logits + row * ld;
+  const long long tgt = targets[row];
+  const bool valid = tgt >= 0 && tgt < V;
+  const float x_t = valid ? to_f32(x[tgt]) : 0.f;
+  const float2* st = reinterpret_cast<const float2*>(tile_stats) + row * n_tiles;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < n_tiles; i += kCeThreads) {
+    const float2 v = st[i];
+    const float mn = fmaxf(m, v.x);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mn) * kLog2e)) + (v.x == -INFINITY ? 0.f : v.y * exp2f((v.x - mn) * kLog2e));
+    m = mn;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mn) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mn) * kLog2e));
+    m = mn;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { s_m[warp] = m; s_s[warp] = s; }
+  __syncthreads();
+  float M = s_m[0];
+#pragma unroll
+  for (int i = 1; i < kCeThreads / 32; ++i) M = fmaxf(M, s_m[i]);
+  float S = 0.f;
+#pragma unroll
+  for (int i = 0; i < kCeThreads / 32; ++i) S += s_m[i] == -INFINITY ? 0.f : s_s[i] * exp2f((s_m[i] - M) * kLog2e);
+  const float lse = M + logf(S);
+  if (threadIdx.x == 0) loss_rows[row] = valid ? lse - x_t : 0.f;
+  row_write_grad<T>(x, V >> 3, tgt, lse, valid ? grad_scale : 0.f);
 }
 
 // Vocabulary-parallel variant, first half: this rank's slice of the row -> stats[row] = (max, sum-exp, target logit or 0).
@@ -188,6 +234,22 @@ extern "C" int nnb_ce_inplace(void* logits, const void* targets, void* loss_rows
     ce_inplace_kernel<T><<<(unsigned)R, kCeThreads, pad, st>>>((T*)logits, (const long long*)targets, (float*)loss_rows, V, ld, grad_scale);
   });
   NNB_LAUNCH_OK("ce_inplace");
+  return 0;
+}
+
+
+// One-sweep cross-entropy on logits whose per-tile statistics came out of the head GEMM (nnb_gemm_ce_stats):
+// tile_stats fp32 [R, n_tiles, 2]. Same outputs as nnb_ce_inplace.
+extern "C" int nnb_ce_grad_from_stats(void* logits, const void* targets, const void* tile_stats, int n_tiles, void* loss_rows,
+                                      long long R, int V, long long ld, float grad_scale, int dtype, cudaStream_t st) {
+  NNB_REQUIRE(V % 8 == 0 && V > 0 && n_tiles > 0, "ce_from_stats: V=%d must be a positive multiple of 8", V);
+  NNB_REQUIRE(ld % 8 == 0 && nnb_aligned16(logits) && nnb_aligned16(tile_stats), "ce_from_stats: rows must be 16-byte aligned");
+  if (R == 0) return 0;
+  NNB_DISPATCH_16(dtype, T, {
+    ce_grad_from_stats_kernel<T><<<(unsigned)R, kCeThreads, 0, st>>>((T*)logits, (const long long*)targets, (const float*)tile_stats,
+                                                                     n_tiles, (float*)loss_rows, V, ld, grad_scale);
+  });
+  NNB_LAUNCH_OK("ce_grad_from_stats");
   return 0;
 }
 

@@ -12,11 +12,14 @@
 //   nnb_allgather_bytes     every rank's shard into the local full buffer (pull).
 //
 // Synchronisation: a second symmetric buffer of uint32 flags, one slot per (phase, block, source
-// rank), written with st.release.sys and polled locally with ld.acquire.sys; values are the call's
-// epoch number, so flags never need resetting (and CUDA-graph replays would need none either).
+// rank), written with st.release.sys and polled locally with ld.acquire.sys; values are epoch
+// numbers that block b of every rank keeps in device memory and bumps once per launch, so flags never
+// need resetting and the launch arguments are the same from call to call (a captured CUDA graph
+// replays the collectives as they are).
 // Block b of a rank only ever talks to block b of its peers, so the kernel needs no grid-wide sync.
-// EVERY wait is bounded: after kPollLimit polls the block records {code, rank, peer, block, epoch} in
-// the status words and carries on to the end, and the host raises after the next synchronisation.
+// EVERY wait is bounded in time (30 s by default): when it runs out the block records
+// {code, rank, peer, block, epoch} in the status words and carries on to the end; the training step
+// reads the status word with its loss and raises on the host.
 // Nothing here waits on a kernel of the same GPU: one rank = one process = one GPU.
 //
 // The reference reaches NCCL through torch DDP / FSDP2 / DTensor (nanonemo/distributed/*.py).
@@ -41,17 +44,28 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// WMAX = compile-time bound on the world size, U = independent 16-byte positions per thread: U x WMAX peer
-// loads are issued before the first add, so each thread keeps 1 KB in flight over NVLink (the kernel is
-// latency-bound otherwise: one load per peer per thread reached only a third of NCCL's bus bandwidth).
+// WMAX = compile-time bound on the world size, U = independent 16-byte positions per thread: U x WMAX peer loads are issued
+// before the first add. U x WMAX = 8 keeps the kernel within 85 registers (see kCommThreads); one block per SM then has
+// 148 x 256 x 128 B = 4.8 MB in flight, above the NVLink latency-bandwidth product (~3 us x 0.8 TB/s).
+//
+// Gradient all-reduce (data parallel): in-place two-shot all-reduce of [lo, lo + n) fused with the 1/world average; rank r
+// reduces slice r, writes the result into every peer's buffer and, on the way, sums the squares of its slice. Each block
+// stores its partial sum of squares into EVERY peer's `norm_parts` row for this bucket ([bucket][rank][block], plain peer
+// stores before the closing barrier), so that after the last bucket every rank holds the same table and adds it up in the
+// same order (nnb_sumsq_combine): the global gradient norm needs no pass over the gradient and no further collective, and
+// it is bitwise identical on every rank.
 template <int WMAX, int U>
-__global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, float* mc, int rank, int world, long long lo,
-                                                                     long long n, float scale, uint32_t epoch, int* status) {
-  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);  // every peer's inputs are final
+__global__ void __launch_bounds__(kCommThreads, 3) allreduce_f32_kernel(Peers P, Peers NP, float* mc, int rank, int world, long long lo,
+                                                                        long long n, float scale, uint32_t* epochs, int slot_blocks,
+                                                                        int bucket, unsigned long long timeout_ns, int* status) {
+  __shared__ float s_part[kCommThreads / 32];
+  const uint32_t epoch = next_block_epoch(epochs);
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // every peer's inputs are final
   const long long per = ((n + world - 1) / world + 3) & ~3LL;       // slice length, multiple of 4
   const long long s0 = min((long long)rank * per, n), s1 = min(s0 + per, n);
   const long long n4 = (s1 - s0) >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  float ss = 0.f;
   if (ok) {
     for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
       float4 v[U][WMAX];
@@ -79,6 +93,7 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, fl
             if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
         }
         acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
         if (mc != nullptr) {
           multimem_st_f4(mc + off, acc);
         } else {
@@ -89,16 +104,45 @@ __global__ void __launch_bounds__(kCommThreads) allreduce_f32_kernel(Peers P, fl
       }
     }
   }
-  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);  // every peer's results have landed here
+  if (NP.data[0] != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v = threadIdx.x < kCommThreads / 32 ? s_part[threadIdx.x] : 0.f;
+      v = warp_sum(v);  // fixed tree: the same inputs give the same bits
+      const long long slot = ((long long)bucket * world + rank) * slot_blocks + blockIdx.x;
+      if ((int)threadIdx.x < world) static_cast<float*>(NP.data[threadIdx.x])[slot] = v;
+    }
+  }
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // every peer's results (and partial norms) have landed here
+}
+
+// out[0] = sum of parts[0 .. n) added in index order by one thread per 1/256th and a fixed tree: same table, same bits.
+__global__ void __launch_bounds__(256) sumsq_combine_kernel(const float* __restrict__ parts, long long n, float* __restrict__ out) {
+  __shared__ float s_part[8];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += 256) s += parts[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += s_part[i];
+    out[0] = t;
+  }
 }
 
 // out[i] = scale * sum_r data[r][lo + rank*per + i]; sumsq_out += sum(out^2) (one atomic per block).
 template <int WMAX, int U>
-__global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers P, float* out, float* sumsq_out, int rank, int world,
-                                                                          long long lo, long long per, float scale,
-                                                                          uint32_t epoch, int* status) {
+__global__ void __launch_bounds__(kCommThreads, 3) reduce_scatter_f32_kernel(Peers P, float* out, float* sumsq_out, int rank, int world,
+                                                                             long long lo, long long per, float scale,
+                                                                             uint32_t* epochs, int slot_blocks,
+                                                                             unsigned long long timeout_ns, int* status) {
   __shared__ float s_part[kCommThreads / 32];
-  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);
+  const uint32_t epoch = next_block_epoch(epochs);
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);
   const long long n4 = per >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   float ss = 0.f;
@@ -136,14 +180,15 @@ __global__ void __launch_bounds__(kCommThreads) reduce_scatter_f32_kernel(Peers 
     }
   }
   // peers may overwrite their inputs only after everybody has read them
-  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);
 }
 
 // local_full[r*per_bytes .. ] = peer r's shard (its bytes [src_off, src_off + per_bytes) ), 16-byte units.
-__global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_t* local_full, int rank, int world,
-                                                                 long long src_off, long long per_bytes, uint32_t epoch,
-                                                                 int* status) {
-  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, gridDim.x, epoch, status);  // every peer's shard is final
+__global__ void __launch_bounds__(kCommThreads, 3) allgather_kernel(Peers P, uint8_t* local_full, int rank, int world,
+                                                                    long long src_off, long long per_bytes, uint32_t* epochs,
+                                                                    int slot_blocks, unsigned long long timeout_ns, int* status) {
+  const uint32_t epoch = next_block_epoch(epochs);
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // every peer's shard is final
   const long long n16 = per_bytes >> 4;
   if (ok) {
     for (int rr = 0; rr < world; ++rr) {
@@ -164,7 +209,7 @@ __global__ void __launch_bounds__(kCommThreads) allgather_kernel(Peers P, uint8_
       }
     }
   }
-  block_barrier(P, rank, world, 1, blockIdx.x, gridDim.x, epoch, status);  // shards may be rewritten once everybody has copied them
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // shards may be rewritten once everybody has copied them
 }
 
 // Exercises the bounded wait: a "world" of two ranks whose flag buffers are both this GPU's buffer, so the
@@ -187,52 +232,77 @@ extern "C" int nnb_comm_timeout_probe(void* flags, void* status, void* result, i
   return 0;
 }
 
-// Flag buffer requirement: uint32 [2 phases][blocks][16] per rank, zero before the first call.
+// Flag buffer requirement: uint32 [2 phases][blocks][16] per rank, zero before the first call; `epochs`: device uint32
+// [blocks], zero before the first call, private to the rank. `blocks` is the count both were sized for; every kernel that
+// shares them indexes its flag slots with it.
 extern "C" int nnb_comm_flag_words(int blocks) { return 2 * blocks * kMaxWorld; }
 
-extern "C" int nnb_allreduce_f32(void* const* data_ptrs, void* const* flag_ptrs, void* multicast_ptr, void* status, int rank,
-                                 int world, long long lo, long long n, float scale, int epoch, int blocks, cudaStream_t st) {
-  Peers P;
+static inline unsigned long long timeout_ns_of(double seconds) {
+  return seconds > 0 ? (unsigned long long)(seconds * 1e9) : kDefaultTimeoutNs;
+}
+
+// norm_ptrs: null, or every rank's `norm_parts` buffer (fp32 [buckets][world][blocks], symmetric); `bucket` picks the row.
+extern "C" int nnb_allreduce_f32(void* const* data_ptrs, void* const* flag_ptrs, void* const* norm_ptrs, void* multicast_ptr,
+                                 void* status, void* epochs, int rank, int world, long long lo, long long n, float scale, int bucket,
+                                 int blocks, double timeout_s, cudaStream_t st) {
+  Peers P, NP;
   if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  if (fill_peers(NP, norm_ptrs, flag_ptrs, world) != 0) return -1;
   NNB_REQUIRE(lo % 4 == 0 && n % 4 == 0, "allreduce: range must be 16-byte aligned (lo=%lld n=%lld)", lo, n);
-  NNB_REQUIRE(blocks > 0 && blocks <= 1024, "allreduce: bad block count %d", blocks);
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "allreduce: bad block count %d or no epoch counters", blocks);
   if (n == 0) return 0;
   NNB_REQUIRE(world <= 8, "allreduce: world %d > 8 not supported by the unrolled kernel", world);
   float* mc = static_cast<float*>(multicast_ptr);
   int* stw = static_cast<int*>(status);
-  if (world <= 2) allreduce_f32_kernel<2, 8><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
-  else if (world <= 4) allreduce_f32_kernel<4, 4><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
-  else allreduce_f32_kernel<8, 2><<<blocks, kCommThreads, 0, st>>>(P, mc, rank, world, lo, n, scale, (uint32_t)epoch, stw);
+  uint32_t* ep = static_cast<uint32_t*>(epochs);
+  const unsigned long long tns = timeout_ns_of(timeout_s);
+  if (world <= 2) allreduce_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
+  else if (world <= 4) allreduce_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
+  else allreduce_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
   NNB_LAUNCH_OK("allreduce_f32");
   return 0;
 }
 
+// out[0] = sum of the first n entries of `parts` in a fixed order (the table the all-reduce kernels filled).
+extern "C" int nnb_sumsq_combine(const void* parts, long long n, void* out, cudaStream_t st) {
+  NNB_REQUIRE(n >= 0 && out != nullptr, "sumsq_combine: bad arguments");
+  sumsq_combine_kernel<<<1, 256, 0, st>>>(static_cast<const float*>(parts), n, static_cast<float*>(out));
+  NNB_LAUNCH_OK("sumsq_combine");
+  return 0;
+}
+
 extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_ptrs, void* out, void* sumsq_out, void* status,
-                                      int rank, int world, long long lo, long long per, float scale, int epoch, int blocks,
-                                      cudaStream_t st) {
+                                      void* epochs, int rank, int world, long long lo, long long per, float scale, int blocks,
+                                      double timeout_s, cudaStream_t st) {
   Peers P;
   if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
   NNB_REQUIRE(lo % 4 == 0 && per % 4 == 0, "reduce_scatter: range must be 16-byte aligned");
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "reduce_scatter: bad block count %d or no epoch counters", blocks);
   if (per == 0) return 0;
   NNB_REQUIRE(world <= 8, "reduce_scatter: world %d > 8 not supported by the unrolled kernel", world);
   float* o = static_cast<float*>(out);
   float* sq = static_cast<float*>(sumsq_out);
   int* stw = static_cast<int*>(status);
-  if (world <= 2) reduce_scatter_f32_kernel<2, 8><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
-  else if (world <= 4) reduce_scatter_f32_kernel<4, 4><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
-  else reduce_scatter_f32_kernel<8, 2><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, (uint32_t)epoch, stw);
+  uint32_t* ep = static_cast<uint32_t*>(epochs);
+  const unsigned long long tns = timeout_ns_of(timeout_s);
+  if (world <= 2) reduce_scatter_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
+  else if (world <= 4) reduce_scatter_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
+  else reduce_scatter_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
   NNB_LAUNCH_OK("reduce_scatter_f32");
   return 0;
 }
 
-extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptrs, void* local_full, void* status, int rank,
-                                   int world, long long src_off, long long per_bytes, int epoch, int blocks, cudaStream_t st) {
+extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptrs, void* local_full, void* status, void* epochs,
+                                   int rank, int world, long long src_off, long long per_bytes, int blocks, double timeout_s,
+                                   cudaStream_t st) {
   Peers P;
   if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
   NNB_REQUIRE(src_off % 16 == 0 && per_bytes % 16 == 0 && nnb_aligned16(local_full), "allgather: 16-byte alignment required");
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "allgather: bad block count %d or no epoch counters", blocks);
   if (per_bytes == 0) return 0;
   allgather_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<uint8_t*>(local_full), rank, world, src_off, per_bytes,
-                                                    (uint32_t)epoch, static_cast<int*>(status));
+                                                    static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
+                                                    static_cast<int*>(status));
   NNB_LAUNCH_OK("allgather");
   return 0;
 }

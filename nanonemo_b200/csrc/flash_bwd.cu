@@ -47,6 +47,11 @@ struct BParams {
   const float* delta;  // [B, H, T]
   uint32_t idesc_s, idesc_dkv, idesc_dq;
   int* status;
+  // Optional inverse RoPE on dK (and on dQ in the convert kernel): fp32 tables [T, 32] of the forward rotation. When given,
+  // the attention inputs were rotated by the producer of Q / K and the gradients leave here un-rotated, i.e. with respect to
+  // the projection before RoPE, so no separate inverse-RoPE pass over the packed gradient is needed.
+  const float* rope_cos;
+  const float* rope_sin;
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -267,6 +272,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_32x32b_x32(t_lane + (half == 0 ? kColdV : kColdK), r0);
       tmem_ld_32x32b_x32(t_lane + (half == 0 ? kColdV : kColdK) + 32, r1);
       tmem_ld_wait();
+      if (half == 1 && p.rope_cos != nullptr && kt * BKV + row < p.T) {
+        // dK of key position t leaves through the transpose of the forward rotation: lo' = lo c + hi s, hi' = hi c - lo s
+        const float* cr = p.rope_cos + (size_t)(kt * BKV + row) * (HD / 2);
+        const float* sr = p.rope_sin + (size_t)(kt * BKV + row) * (HD / 2);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 c4 = __ldg(reinterpret_cast<const float4*>(cr + i)), s4 = __ldg(reinterpret_cast<const float4*>(sr + i));
+          const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float lo = __uint_as_float(r0[i + e]), hi = __uint_as_float(r1[i + e]);
+            r0[i + e] = __float_as_uint(lo * cc[e] + hi * ss[e]);
+            r1[i + e] = __float_as_uint(hi * cc[e] - lo * ss[e]);
+          }
+        }
+      }
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         uint32_t w[4];
@@ -335,21 +356,37 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   if (w < rows && sub == 0) delta[((size_t)b * H + h) * T + t] = s;
 }
 
-// dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous)
+// dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous); with tables, the inverse RoPE of position t is
+// applied on the way (columns j and j + 32 are partners, so one thread converts 8 + 8 elements).
 __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int H,
-                                        int T, long long sb, long long st, long long sh) {
-  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;  // one thread per 8 elements
-  const long long total = rows * (HD / 8);
+                                        int T, long long sb, long long st, long long sh, const float* __restrict__ rope_cos,
+                                        const float* __restrict__ rope_sin) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;  // one thread per 8 + 8 elements
+  const long long total = rows * (HD / 16);
   if (idx >= total) return;
-  const long long r = idx / (HD / 8);
-  const int j = (int)(idx % (HD / 8)) * 8;
+  const long long r = idx / (HD / 16);
+  const int j = (int)(idx % (HD / 16)) * 8;
   const int h = (int)(r % H);
   const long long bt = r / H;
   const int t = (int)(bt % T);
   const long long b = bt / T;
-  float v[8];
-  Chunk8<float>::load(acc + r * HD + j, v);
-  Chunk8<__nv_bfloat16>::store(dq + b * sb + t * st + h * sh + j, v);
+  float lo[8], hi[8];
+  Chunk8<float>::load(acc + r * HD + j, lo);
+  Chunk8<float>::load(acc + r * HD + HD / 2 + j, hi);
+  if (rope_cos != nullptr) {
+    float c[8], s[8];
+    Chunk8<float>::load(rope_cos + (size_t)t * (HD / 2) + j, c);
+    Chunk8<float>::load(rope_sin + (size_t)t * (HD / 2) + j, s);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = lo[i], bb = hi[i];
+      lo[i] = a * c[i] + bb * s[i];
+      hi[i] = bb * c[i] - a * s[i];
+    }
+  }
+  __nv_bfloat16* dst = dq + b * sb + t * st + h * sh;
+  Chunk8<__nv_bfloat16>::store(dst + j, lo);
+  Chunk8<__nv_bfloat16>::store(dst + HD / 2 + j, hi);
 }
 
 }  // namespace
@@ -366,13 +403,15 @@ extern "C" int nnb_flash_bwd_prof_read(unsigned long long* out) { return (int)cu
 // All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16.
 // lse: fp32 [B, H, T] from the forward pass; delta: fp32 [B, H, T] scratch (written here);
 // dq_acc: fp32 [B, T, H, hd] contiguous scratch (cleared by the delta pre-pass; partial tiles are reduce-added into it).
+// rope_cos / rope_sin: null, or fp32 [T, 32] tables: dQ and dK are then returned through the inverse rotation (head_dim 64).
 extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
                              void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, int hd,
                              long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st, long long k_sh,
                              long long v_sb, long long v_st, long long v_sh, long long o_sb, long long o_st, long long o_sh,
                              long long do_sb, long long do_st, long long do_sh, long long dq_sb, long long dq_st,
                              long long dq_sh, long long dk_sb, long long dk_st, long long dk_sh, long long dv_sb,
-                             long long dv_st, long long dv_sh, float scale, int dtype, void* status, cudaStream_t st) {
+                             long long dv_st, long long dv_sh, float scale, int dtype, const void* rope_cos, const void* rope_sin,
+                             void* status, cudaStream_t st) {
   NNB_REQUIRE(hd == HD || hd == 128, "flash_bwd: head_dim %d not supported (64, 128)", hd);
   NNB_REQUIRE(dtype == NNB_BF16, "flash_bwd: bf16 only");
   NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_bwd: bad shape");
@@ -380,6 +419,9 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   // (NANONEMO_FLASH_BWD=transposed), but there the 128 x 128 formulation of this file measured faster (0.43 vs 0.57 ms at
   // B32 H12/4 T1024): with 64-wide tiles every MMA has N = 64 and is bound by shared-memory operand reads.
   static const bool square = [] { const char* e = getenv("NANONEMO_FLASH_BWD"); return !(e && e[0] == 't'); }();
+  NNB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "flash_bwd: give both RoPE tables or neither");
+  NNB_REQUIRE(rope_cos == nullptr || (hd == HD && square && nnb_aligned16(rope_cos) && nnb_aligned16(rope_sin)),
+              "flash_bwd: the fused inverse RoPE exists for head_dim 64 on the 128 x 128 kernel only");
   if (hd == 128 || !square) {
     const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh}, os[3] = {o_sb, o_st, o_sh};
     const long long dos[3] = {do_sb, do_st, do_sh}, dqs[3] = {dq_sb, dq_st, dq_sh}, dks[3] = {dk_sb, dk_st, dk_sh};
@@ -415,6 +457,8 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   p.idesc_dkv = sm100::make_idesc_f16(1, 1, 1, BKV, HD);
   p.idesc_dq = sm100::make_idesc_f16(1, 0, 1, BQ, HD);
   p.status = static_cast<int*>(status);
+  p.rope_cos = static_cast<const float*>(rope_cos);
+  p.rope_sin = static_cast<const float*>(rope_sin);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
@@ -426,8 +470,8 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   dim3 grid((T + BKV - 1) / BKV, KVH, B);
   flash_bwd_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   NNB_LAUNCH_OK("flash_bwd");
-  flash_dq_convert_kernel<<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows,
-                                                                                    H, T, dq_sb, dq_st, dq_sh);
+  flash_dq_convert_kernel<<<(unsigned)((rows * (HD / 16) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows,
+                                                                                     H, T, dq_sb, dq_st, dq_sh, p.rope_cos, p.rope_sin);
   NNB_LAUNCH_OK("flash_dq_convert");
   return 0;
 }

@@ -239,9 +239,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (p.mode == 2 && m_blk / p.mblocks_per_rank != p.rank) {
           // rows of a peer: wait until a gather CTA has landed this m-block in the local buffer
           const uint32_t* flag = p.local_flags + 2 + m_blk;
-          uint32_t polls = 0;
+          nnbcomm::Deadline dl;
           while ((int32_t)(nnbcomm::ld_acquire_gpu(flag) - p.epoch) < 0) {
-            if (++polls > nnbcomm::kPollLimit || *abort_flag) { ok = false; *abort_flag = 1; fail_role = 4; fail_item = item; break; }
+            if (dl.expired() || *abort_flag) { ok = false; *abort_flag = 1; fail_role = 4; fail_item = item; break; }
             __nanosleep(32);
           }
           if (!ok) break;
@@ -361,9 +361,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();  // the store that last read `buf` is done
         if (!go) {
           if (et == 0) {
-            uint32_t polls = 0;
-            while ((int32_t)(nnbcomm::ld_acquire_gpu(p.local_flags) - p.epoch) < 0 && ++polls < nnbcomm::kPollLimit) __nanosleep(64);
-            if (polls >= nnbcomm::kPollLimit) *abort_flag = 1;
+            nnbcomm::Deadline dl;
+            bool late = false;
+            while ((int32_t)(nnbcomm::ld_acquire_gpu(p.local_flags) - p.epoch) < 0 && !(late = dl.expired())) __nanosleep(64);
+            if (late) *abort_flag = 1;
           }
           go = true;
         }
@@ -616,6 +617,46 @@ extern "C" int nnb_gemm_bf16(const void* A, const void* B, void* D, int M, int N
                              int bn_hint, int max_ctas, void* status, cudaStream_t st) {
   return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, dtype, out_f32, accumulate, k_splits, bn_hint, max_ctas, status,
                    nullptr, st);
+}
+
+// ---- GEMMs with a fused epilogue (CTA-pair kernel only; return code 1 = shape not served, the caller runs the unfused ops)
+static int fused_gemm_common(NnbGemm2Args& g, const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                             long long ldb, long long ldd, int dtype, void* status) {
+  NNB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %dx%dx%d", M, N, K);
+  NNB_REQUIRE(dtype == NNB_BF16 || dtype == NNB_F16, "gemm: inputs must be bf16 or fp16 (dtype code %d)", dtype);
+  g.A = A; g.B = B; g.D = D; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb; g.ldd = ldd;
+  g.a_mn = 0; g.b_mn = 0; g.dtype = dtype; g.out_f32 = 0; g.accumulate = 0; g.k_splits = 1; g.max_ctas = 0; g.status = status;
+  return 0;
+}
+
+// gu[M, 2F] = x[M, K] @ w_gu[2F, K]^T (gate rows first, then up rows) and act[M, F] = silu(gate) * up, one kernel.
+extern "C" int nnb_gemm_swiglu(const void* X, const void* Wgu, void* GU, void* ACT, int M, int F, int K, long long lda, long long ldw,
+                               long long ldgu, long long ldact, int dtype, void* status, cudaStream_t st) {
+  NnbGemm2Args g{};
+  if (int rc = fused_gemm_common(g, X, Wgu, GU, M, 2 * F, K, lda, ldw, ldgu, dtype, status)) return rc;
+  g.epilogue = EPI_SWIGLU; g.E = ACT; g.lde = ldact;
+  return nnb_gemm2_launch(g, st);
+}
+
+// qkv[M, N] = x[M, K] @ w[N, K]^T with rotate-half RoPE applied to columns [0, rope_cols) (heads of head_dim columns, row m
+// at position m % t_len; cos / sin: fp32 [t_len, head_dim / 2]); the remaining columns (V) pass through.
+extern "C" int nnb_gemm_rope(const void* X, const void* W, void* QKV, const void* cos_t, const void* sin_t, int M, int N, int K,
+                             long long lda, long long ldw, long long ldd, int t_len, int rope_cols, int head_dim, int dtype,
+                             void* status, cudaStream_t st) {
+  NnbGemm2Args g{};
+  if (int rc = fused_gemm_common(g, X, W, QKV, M, N, K, lda, ldw, ldd, dtype, status)) return rc;
+  g.epilogue = EPI_ROPE; g.cos_t = cos_t; g.sin_t = sin_t; g.t_len = t_len; g.rope_cols = rope_cols; g.head_dim = head_dim;
+  return nnb_gemm2_launch(g, st);
+}
+
+// logits[M, N] = x[M, K] @ w[N, K]^T (16-bit) plus stats[M, ceil(N / 256), 2] = (max, sum of exp(x - max)) of every
+// 256-column tile of every row, computed on the stored (rounded) logits. N must be a multiple of 64.
+extern "C" int nnb_gemm_ce_stats(const void* X, const void* W, void* logits, void* stats, int M, int N, int K, long long lda,
+                                 long long ldw, long long ldd, int dtype, void* status, cudaStream_t st) {
+  NnbGemm2Args g{};
+  if (int rc = fused_gemm_common(g, X, W, logits, M, N, K, lda, ldw, ldd, dtype, status)) return rc;
+  g.epilogue = EPI_CE_STATS; g.stats = stats;
+  return nnb_gemm2_launch(g, st);
 }
 
 // GEMM -> reduce-scatter in one kernel (row-parallel linear under tensor + sequence parallelism):

@@ -12,6 +12,19 @@
 // Roles per CTA as in gemm.cu: warp 0 TMA producer, warp 1 MMA issuer (leader only; both allocate TMEM), warps 2..5
 // epilogue (tcgen05.ld -> swizzled staging -> TMA store / reduce-add). All waits are bounded.
 // Replaces the cuBLAS calls behind nn.Linear in the reference (nanonemo/model/layers.py:80-83, 128-130).
+//
+// Fused epilogues (template parameter EPI), each replacing a separate pass over HBM of the reference's elementwise kernels:
+//   EPI_SWIGLU    gate||up projection: the leader stages 128 GATE rows of the weight, its peer the matching 128 UP rows, so
+//                 one accumulator holds gate (columns 0..127) and up (128..255) of the same 128 features; the epilogue
+//                 writes both halves of the projection (kept for backward) AND act = silu(gate) * up
+//                 (nanonemo/kernels/triton/swiglu.py:19-38).
+//   EPI_ROPE      QKV projection: rotate-half RoPE applied to the query / key heads while the tile leaves tensor memory
+//                 (one cos / sin row per token; a 64-column chunk is one head, two chunks at head_dim 128)
+//                 (nanonemo/kernels/triton/rope.py:18-47).
+//   EPI_CE_STATS  LM head: besides the 16-bit logits, every (row, 256-column tile) gets its (max, sum of exp(x - max)), so
+//                 the cross-entropy kernel needs one sweep over the logits instead of two
+//                 (nanonemo/kernels/triton/linear_ce.py:21-41).
+// All three compute on the values ROUNDED to the 16-bit output type, so they match the unfused kernels bit for bit.
 #include "gemm2.cuh"
 
 #include "common.cuh"
@@ -26,11 +39,15 @@ constexpr int BN = 256;   // columns per pair tile; each CTA stages BN / 2 rows 
 constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr int kEpilogueThreads = 128;
-constexpr int kStages = 6;
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = (BN / 2) * BK * 2, kStageBytes = kStageBytesA + kStageBytesB;
-constexpr int kStagingBytes = 2 * BM * 128;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+// The SwiGLU epilogue fills three staging tiles at once (gate, up, act): one stage less for the operand ring.
+template <int EPI> struct Cfg {
+  static constexpr int kStages = EPI == EPI_SWIGLU ? 5 : 6;
+  static constexpr int kStagingTiles = EPI == EPI_SWIGLU ? 3 : 2;
+  static constexpr int kStagingBytes = kStagingTiles * BM * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
 
 struct Params2 {
   int M, N, K;
@@ -39,7 +56,56 @@ struct Params2 {
   int a_mn, b_mn, out_f32, reduce_add, out_bf16;
   uint32_t idesc;
   int* status;
+  // fused epilogues
+  int epi_cols;        // EPI_SWIGLU: F (the up rows of the weight start at row F); EPI_ROPE: columns that are rotated
+  int t_len, half_dim; // EPI_ROPE: sequence length (row m uses table row m % t_len), head_dim / 2
+  const float* cos_t;  // EPI_ROPE: [t_len, half_dim] fp32
+  const float* sin_t;
+  float* stats;        // EPI_CE_STATS: [M, n_blocks, 2] fp32 (max, sum of exp(x - max)) per 256-column tile
 };
+
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf) {
+  if (bf) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack16(uint32_t w, bool bf) {
+  if (bf) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
+  return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+__device__ __forceinline__ float round16(float x, bool bf) {
+  return bf ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
+}
+// 32 consecutive columns (16 packed words) of this thread's row into 16-byte units [u0, u0 + 4) of a swizzled staging row.
+__device__ __forceinline__ void stage32(uint8_t* my_row, int sw, int u0, const uint32_t (&w)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(my_row + (((u0 + j) ^ sw) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+// Rotate-half on 32 (lo, hi) column pairs of one token: lo' = lo c - hi s, hi' = lo s + hi c, computed on the rounded values.
+__device__ __forceinline__ void rope32(uint32_t (&lo)[32], uint32_t (&hi)[32], const float (&cc)[32], const float (&ss)[32], bool bf) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float a = round16(__uint_as_float(lo[i]), bf), b = round16(__uint_as_float(hi[i]), bf);
+    lo[i] = __float_as_uint(a * cc[i] - b * ss[i]);
+    hi[i] = __float_as_uint(a * ss[i] + b * cc[i]);
+  }
+}
+// 32 consecutive fp32 table entries of one token (16-byte aligned: the tables have 32 or 64 entries per row).
+__device__ __forceinline__ void load_table32(const float* __restrict__ src, float (&dst)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(src + i));
+    dst[i] = v.x; dst[i + 1] = v.y; dst[i + 2] = v.z; dst[i + 3] = v.w;
+  }
+}
+__device__ __forceinline__ void pack32(const uint32_t (&r)[32], uint32_t (&w)[16], bool bf) {
+#pragma unroll
+  for (int e = 0; e < 16; ++e) w[e] = pack16(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]), bf);
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -80,9 +146,11 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmD, const Params2 p) {
+                     const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmE, const Params2 p) {
+  constexpr int kStages = Cfg<EPI>::kStages, kStagingBytes = Cfg<EPI>::kStagingBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
@@ -118,6 +186,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmD);
+    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmE);
   }
   tc_fence_before();
   __syncthreads();
@@ -147,7 +216,8 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int m_pair, n_blk;
         tile_coords(tile, m_pair, n_blk);
         const int m_row0 = (m_pair * 2 + (int)rank) * BM;
-        const int n_row0 = n_blk * BN + (int)rank * (BN / 2);
+        // SwiGLU: the leader stages gate rows, the peer the up rows (F further down) of the same 128 features
+        const int n_row0 = EPI == EPI_SWIGLU ? n_blk * (BN / 2) + (int)rank * p.epi_cols : n_blk * BN + (int)rank * (BN / 2);
         const int kb0 = ks * p.kblocks_per_split, kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
@@ -217,6 +287,14 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tile_coords(tile, m_pair, n_blk);
       const int d_row = (m_pair * 2 + (int)rank) * BM;
       const uint32_t acc = tile_iter & 1, acc_ph = (tile_iter >> 1) & 1;
+      float rope_c[32], rope_s[32];  // EPI_ROPE, head_dim 64: this token's table row, fetched while the tile is still being multiplied
+      if constexpr (EPI == EPI_ROPE) {
+        if (p.half_dim == 32 && n_blk * BN < p.epi_cols) {
+          const int t = (d_row + row) % p.t_len;
+          load_table32(p.cos_t + (size_t)t * 32, rope_c);
+          load_table32(p.sin_t + (size_t)t * 32, rope_s);
+        }
+      }
       const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag);
       if (!ok) { fail_role = 3; fail_item = item; }
       if (et == 0) *epi_abort = *abort_flag;
@@ -224,57 +302,173 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       if (*epi_abort) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      const int cols_per_chunk = p.out_f32 ? 32 : 64;
-      const int chunks = BN / cols_per_chunk;
       const bool rows_live = d_row < p.M;  // an odd number of 128-row blocks leaves the peer's last block outside the matrix
-      for (int c = 0; c < chunks && rows_live; ++c) {
-        const int col0 = c * cols_per_chunk;
-        if (n_blk * BN + col0 >= p.N) break;
-        uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
-        ++gchunk;
-        if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
-        named_barrier_sync(1, kEpilogueThreads);
-        uint8_t* my_row = buf + row * 128;
-        const int sw = row & 7;
-        if (p.out_f32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + col0, r);
-          tmem_ld_wait();
+      const bool bf = p.out_bf16 != 0;
+      const int sw = row & 7;
+      if constexpr (EPI == EPI_SWIGLU) {
+        // accumulator columns [0, 128) = gate, [128, 256) = up of features n_blk * 128 ...; 64 features per round, all three
+        // staging tiles (gate | up | act) filled in two half rounds of 32 columns, then three TMA stores
+        const int F = p.epi_cols;
+        for (int c = 0; c < 2 && rows_live; ++c) {
+          const int fcol = n_blk * (BN / 2) + c * 64;
+          if (fcol >= F) break;
+          if (et == 0 && pending_stores > 0) tma_wait_group_read<0>();
+          named_barrier_sync(1, kEpilogueThreads);
+          uint8_t* row_g = staging + row * 128;
+          uint8_t* row_u = row_g + BM * 128;
+          uint8_t* row_a = row_u + BM * 128;
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        } else {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32b_x32(t_row + col0, r0);
-          tmem_ld_32x32b_x32(t_row + col0 + 32, r1);
-          tmem_ld_wait();
-          const bool is_bf16 = p.out_bf16 != 0;
+          for (int h = 0; h < 2; ++h) {
+            uint32_t g[32], u[32], wg[16], wu[16], wa[16];
+            tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, g);
+            tmem_ld_32x32b_x32(t_row + BN / 2 + c * 64 + h * 32, u);
+            tmem_ld_wait();
+            pack32(g, wg, bf);
+            pack32(u, wu, bf);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = (j & 3) * 8 + 2 * e;
-              const float lo = __uint_as_float(j < 4 ? r0[i] : r1[i]), hi = __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]);
-              if (is_bf16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&v);
-              }
+            for (int e = 0; e < 16; ++e) {
+              const float2 gg = unpack16(wg[e], bf), uu = unpack16(wu[e], bf);
+              wa[e] = pack16(gg.x / (1.f + __expf(-gg.x)) * uu.x, gg.y / (1.f + __expf(-gg.y)) * uu.y, bf);
             }
-            *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            stage32(row_g, sw, h * 4, wg);
+            stage32(row_u, sw, h * 4, wu);
+            stage32(row_a, sw, h * 4, wa);
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, kEpilogueThreads);
+          if (et == 0) {
+            tma_store_2d(&tmD, smem_u32(staging), fcol, d_row);
+            tma_store_2d(&tmD, smem_u32(staging + BM * 128), F + fcol, d_row);
+            tma_store_2d(&tmE, smem_u32(staging + 2 * BM * 128), fcol, d_row);
+            tma_commit_group();
+          }
+          pending_stores = 1;
+        }
+      } else if constexpr (EPI == EPI_ROPE) {
+        if (p.half_dim == 32) {
+          // head_dim 64: a 64-column chunk is one head; its two 32-column halves are the rotation partners
+          for (int c = 0; c < BN / 64 && rows_live; ++c) {
+            const int gcol = n_blk * BN + c * 64;
+            if (gcol >= p.N) break;
+            uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
+            ++gchunk;
+            if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
+            named_barrier_sync(1, kEpilogueThreads);
+            uint32_t r0[32], r1[32], w0[16], w1[16];
+            tmem_ld_32x32b_x32(t_row + c * 64, r0);
+            tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
+            tmem_ld_wait();
+            if (gcol < p.epi_cols) rope32(r0, r1, rope_c, rope_s, bf);
+            pack32(r0, w0, bf);
+            pack32(r1, w1, bf);
+            stage32(buf + row * 128, sw, 0, w0);
+            stage32(buf + row * 128, sw, 4, w1);
+            fence_proxy_async_smem();
+            named_barrier_sync(1, kEpilogueThreads);
+            if (et == 0) {
+              tma_store_2d(&tmD, smem_u32(buf), gcol, d_row);
+              tma_commit_group();
+            }
+            if (pending_stores < 2) ++pending_stores;
+          }
+        } else {
+          // head_dim 128: a head is two chunks; column i of the first rotates with column i of the second, so both
+          // staging tiles are filled together (32 column pairs per half round) and stored as two tiles
+          const int t = (d_row + row) % p.t_len;
+          for (int g = 0; g < BN / 128 && rows_live; ++g) {
+            const int gcol = n_blk * BN + g * 128;
+            if (gcol >= p.N) break;
+            if (et == 0 && pending_stores > 0) tma_wait_group_read<0>();
+            named_barrier_sync(1, kEpilogueThreads);
+            uint8_t* row_lo = staging + row * 128;
+            uint8_t* row_hi = row_lo + BM * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t lo[32], hi[32], w0[16], w1[16];
+              tmem_ld_32x32b_x32(t_row + g * 128 + h * 32, lo);
+              tmem_ld_32x32b_x32(t_row + g * 128 + 64 + h * 32, hi);
+              tmem_ld_wait();
+              if (gcol < p.epi_cols) {
+                float cc[32], ss[32];
+                load_table32(p.cos_t + (size_t)t * 64 + h * 32, cc);
+                load_table32(p.sin_t + (size_t)t * 64 + h * 32, ss);
+                rope32(lo, hi, cc, ss, bf);
+              }
+              pack32(lo, w0, bf);
+              pack32(hi, w1, bf);
+              stage32(row_lo, sw, h * 4, w0);
+              stage32(row_hi, sw, h * 4, w1);
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1, kEpilogueThreads);
+            if (et == 0) {
+              tma_store_2d(&tmD, smem_u32(staging), gcol, d_row);
+              tma_store_2d(&tmD, smem_u32(staging + BM * 128), gcol + 64, d_row);
+              tma_commit_group();
+            }
+            pending_stores = 2;
           }
         }
-        fence_proxy_async_smem();
-        named_barrier_sync(1, kEpilogueThreads);
-        if (et == 0) {
-          if (p.reduce_add) tma_reduce_add_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
-          else tma_store_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
-          tma_commit_group();
+      } else {
+        const int cols_per_chunk = p.out_f32 ? 32 : 64;
+        const int chunks = BN / cols_per_chunk;
+        float st_m = -INFINITY, st_s = 0.f;  // EPI_CE_STATS: this row's running (max, sum of exp) over the tile
+        for (int c = 0; c < chunks && rows_live; ++c) {
+          const int col0 = c * cols_per_chunk;
+          if (n_blk * BN + col0 >= p.N) break;
+          uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
+          ++gchunk;
+          if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
+          named_barrier_sync(1, kEpilogueThreads);
+          uint8_t* my_row = buf + row * 128;
+          if (p.out_f32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + col0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          } else {
+            uint32_t r0[32], r1[32], w0[16], w1[16];
+            tmem_ld_32x32b_x32(t_row + col0, r0);
+            tmem_ld_32x32b_x32(t_row + col0 + 32, r1);
+            tmem_ld_wait();
+            pack32(r0, w0, bf);
+            pack32(r1, w1, bf);
+            if constexpr (EPI == EPI_CE_STATS) {
+              constexpr float kLog2e = 1.4426950408889634f;
+              float x[64];
+              float cm = -INFINITY;
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const float2 a = unpack16(w0[e], bf), b = unpack16(w1[e], bf);
+                x[2 * e] = a.x; x[2 * e + 1] = a.y; x[32 + 2 * e] = b.x; x[32 + 2 * e + 1] = b.y;
+                cm = fmaxf(cm, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
+              }
+              if (cm > st_m) {
+                st_s *= exp2f((st_m - cm) * kLog2e);
+                st_m = cm;
+              }
+              const float mb = st_m * kLog2e;
+#pragma unroll
+              for (int i = 0; i < 64; ++i) st_s += exp2f(x[i] * kLog2e - mb);
+            }
+            stage32(my_row, sw, 0, w0);
+            stage32(my_row, sw, 4, w1);
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, kEpilogueThreads);
+          if (et == 0) {
+            if (p.reduce_add) tma_reduce_add_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
+            else tma_store_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
+            tma_commit_group();
+          }
+          if (pending_stores < 2) ++pending_stores;
         }
-        if (pending_stores < 2) ++pending_stores;
+        if constexpr (EPI == EPI_CE_STATS) {
+          if (rows_live && d_row + row < p.M)
+            *reinterpret_cast<float2*>(p.stats + ((size_t)(d_row + row) * p.n_blocks + n_blk) * 2) = make_float2(st_m, st_s);
+        }
       }
       // this CTA's half of the accumulator has been read: tell the leader's MMA thread
       tc_fence_before();
@@ -307,31 +501,63 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 }  // namespace
 
-int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
-  const int sms = a.max_ctas > 0 ? min(a.max_ctas, nnb_num_sms()) : nnb_num_sms();
+namespace {
+
+template <int EPI>
+int max_resident_pairs() {
   static int max_clusters = -1;
   if (max_clusters < 0) {
-    cudaFuncSetAttribute(gemm2_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    auto kern = gemm2_tcgen05_kernel<EPI>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<EPI>::kSmemBytes) != cudaSuccess) {
+      nnb_set_error("gemm2: cannot reserve %d bytes of shared memory", Cfg<EPI>::kSmemBytes);
+      cudaGetLastError();
+      return -3;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * (nnb_num_sms() / 2));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.dynamicSmemBytes = Cfg<EPI>::kSmemBytes;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm2_tcgen05_kernel, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = 0; }
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = 0; }
     max_clusters = n;
   }
-  const int pairs = min(sms / 2, max_clusters);  // persistent pairs must all be resident at once
+  return max_clusters;
+}
+
+template <int EPI>
+int launch2(const NnbGemm2Args& a, cudaStream_t st) {
+  const int sms = a.max_ctas > 0 ? min(a.max_ctas, nnb_num_sms()) : nnb_num_sms();
+  const int resident = max_resident_pairs<EPI>();
+  if (resident < 0) return resident;
+  const int pairs = min(sms / 2, resident);  // persistent pairs must all be resident at once
   if (pairs < 1 || a.M < 2 * BM || a.N < BN / 2) return 1;
   Params2 p{};
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.m_pairs = (a.M + 2 * BM - 1) / (2 * BM);
   p.n_blocks = (a.N + BN - 1) / BN;
   p.kblocks_total = (a.K + BK - 1) / BK;
+  if (EPI == EPI_SWIGLU) {
+    // a.N = 2 F (rows of the gate||up weight); one tile = 128 features = gate and up columns of the same features
+    NNB_REQUIRE(!a.out_f32 && !a.a_mn && !a.b_mn && !a.accumulate && a.E != nullptr, "gemm_swiglu: plain K-major 16-bit problem expected");
+    NNB_REQUIRE(a.N % 256 == 0, "gemm_swiglu: F = %d must be a multiple of 128", a.N / 2);
+    p.epi_cols = a.N / 2;
+    p.n_blocks = p.epi_cols / (BN / 2);
+  } else if (EPI == EPI_ROPE) {
+    NNB_REQUIRE(!a.out_f32 && !a.accumulate, "gemm_rope: 16-bit output expected");
+    NNB_REQUIRE((a.head_dim == 64 || a.head_dim == 128) && a.rope_cols % a.head_dim == 0 && a.N % a.head_dim == 0 && a.t_len > 0 &&
+                    a.cos_t != nullptr && a.sin_t != nullptr && nnb_aligned16(a.cos_t) && nnb_aligned16(a.sin_t),
+                "gemm_rope: head_dim must be 64 or 128, columns whole heads, tables 16-byte aligned");
+    p.epi_cols = a.rope_cols; p.t_len = a.t_len; p.half_dim = a.head_dim / 2;
+    p.cos_t = static_cast<const float*>(a.cos_t); p.sin_t = static_cast<const float*>(a.sin_t);
+  } else if (EPI == EPI_CE_STATS) {
+    NNB_REQUIRE(!a.out_f32 && !a.accumulate && a.N % 64 == 0 && a.stats != nullptr, "gemm_ce_stats: 16-bit output with N a multiple of 64 expected");
+    p.stats = static_cast<float*>(a.stats);
+  }
   int splits = 1;
   if (a.out_f32) {
     if (a.k_splits > 0) splits = a.k_splits;
@@ -362,7 +588,7 @@ int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
   p.idesc = sm100::make_idesc_f16(a.dtype == NNB_BF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN);
   p.status = static_cast<int*>(a.status);
   const CUtensorMapDataType in_dt = a.dtype == NNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUtensorMap tmA, tmB, tmD;
+  CUtensorMap tmA, tmB, tmD, tmE;
   if (!p.a_mn) { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, a.A, a.M, a.K, a.lda * 2, BM, BK, "gemm2 A")) return -4; }
   else         { if (!nnb_make_tmap_2d(&tmA, in_dt, 2, a.A, a.K, a.M, a.lda * 2, BK, 64, "gemm2 A^T")) return -4; }
   if (!p.b_mn) { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, a.B, a.N, a.K, a.ldb * 2, BN / 2, BK, "gemm2 B")) return -4; }
@@ -370,21 +596,27 @@ int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
   const CUtensorMapDataType d_dt = a.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : in_dt;
   const int d_bytes = a.out_f32 ? 4 : 2, d_box = a.out_f32 ? 32 : 64;
   if (!nnb_make_tmap_2d(&tmD, d_dt, d_bytes, a.D, a.M, a.N, a.ldd * d_bytes, BM, d_box, "gemm2 D")) return -4;
+  tmE = tmD;
+  if (EPI == EPI_SWIGLU && !nnb_make_tmap_2d(&tmE, in_dt, 2, a.E, a.M, a.N / 2, a.lde * 2, BM, 64, "gemm2 act")) return -4;
   if (a.out_f32 && !a.accumulate && p.k_splits > 1) {
     if (a.ldd == a.N) cudaMemsetAsync(a.D, 0, (size_t)a.M * a.N * 4, st);
     else cudaMemset2DAsync(a.D, a.ldd * 4, 0, (size_t)a.N * 4, a.M, st);
   }
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm2_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
-      nnb_set_error("gemm2: cannot reserve %d bytes of shared memory", kSmemBytes);
-      return -3;
-    }
-    configured = true;
-  }
   const int items = p.m_pairs * p.n_blocks * p.k_splits;
   const int grid = 2 * min(items, pairs);
-  gemm2_tcgen05_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, tmD, p);
+  gemm2_tcgen05_kernel<EPI><<<grid, kThreads, Cfg<EPI>::kSmemBytes, st>>>(tmA, tmB, tmD, tmE, p);
   NNB_LAUNCH_OK("gemm2_tcgen05");
   return 0;
+}
+
+}  // namespace
+
+int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
+  switch (a.epilogue) {
+    case EPI_NONE: return launch2<EPI_NONE>(a, st);
+    case EPI_SWIGLU: return launch2<EPI_SWIGLU>(a, st);
+    case EPI_ROPE: return launch2<EPI_ROPE>(a, st);
+    case EPI_CE_STATS: return launch2<EPI_CE_STATS>(a, st);
+    default: nnb_set_error("gemm2: unknown epilogue %d", a.epilogue); return -1;
+  }
 }

@@ -43,6 +43,7 @@ class ModelConfig:
     linear_impl: str = "torch"  # torch | sm100 (tcgen05 bf16 GEMM) | mxfp8 (block-scaled fp8; "te" resolves here)
     embed_kernel: str = "torch"
     head_dim_override: int | None = None  # head_dim when it is not d_model / n_heads (1.3B: 16 heads x 128)
+    fuse_epilogues: bool = True  # sm100 path: RoPE / SwiGLU / softmax statistics inside the producing GEMM's epilogue
 
     def __post_init__(self):
         assert self.n_heads % self.n_kv_heads == 0, "query heads must group evenly over KV heads"

@@ -91,6 +91,8 @@ class Attention(nn.Module):
         self.wqkv = make_linear(cfg, cfg.d_model, self.q_dim + 2 * self.kv_dim)
         self.wo = make_linear(cfg, self.q_dim, cfg.d_model)
         self.rope_impl, self.attn_impl = r.rope_kernel, r.attn_kernel
+        # one autograd node for projection + RoPE (GEMM epilogue) + attention when all three run on the sm100 kernels
+        self.fused = cfg.fuse_epilogues and r.linear_impl == "sm100" and self.rope_impl == "sm100" and self.attn_impl == "sm100"
         self.tp = None  # parallel.tp.TPContext once the model has been sharded
 
     def split_qkv(self):
@@ -126,6 +128,9 @@ class Attention(nn.Module):
 
     def _attend(self, x, cos, sin, qkv=None, project=True):
         H, KVH, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        if qkv is None and self.fused and x.is_cuda and ops.fused_ok():
+            y = ops.qkv_rope_attention(x, self.wqkv.weight, cos, sin, H, KVH, hd)
+            return self.wo(y) if project else y
         if qkv is None:
             qkv = self.wqkv(x)  # (B, T, (H + 2 KVH) hd)
         B, T, _ = qkv.shape
@@ -158,6 +163,7 @@ class MLP(nn.Module):
         self.w_gu = make_linear(cfg, cfg.d_model, 2 * cfg.d_ff)  # rows [0, d_ff) = gate, [d_ff, 2 d_ff) = up
         self.w_down = make_linear(cfg, cfg.d_ff, cfg.d_model)
         self.act_impl = r.swiglu_kernel
+        self.fused = cfg.fuse_epilogues and r.linear_impl == "sm100" and self.act_impl == "sm100"
         self.tp = None
 
     def split_gu(self):
@@ -173,6 +179,8 @@ class MLP(nn.Module):
                 return row_parallel_linear(act, self.w_down.weight, ft)
             full = self.tp.gather_tokens(x)
             return self.tp.scatter_tokens(self.w_down(ops.swiglu_packed(self.w_gu(full), impl=self.act_impl)))
+        if self.fused and x.is_cuda and ops.fused_ok():
+            return self.w_down(ops.linear_swiglu(x, self.w_gu.weight))
         return self.w_down(ops.swiglu_packed(self.w_gu(x), impl=self.act_impl))
 
 

@@ -155,6 +155,29 @@ def swiglu_packed(gu, impl="torch"):
     return f(gu)
 
 
+def fused_ok() -> bool:
+    """The block-level fused operators compute in bf16 (the attention kernels are bf16 only)."""
+    from nanonemo_b200.ops.gemm import compute_dtype
+
+    return compute_dtype() == torch.bfloat16
+
+
+def qkv_rope_attention(x, weight, cos, sin, n_heads, n_kv_heads, head_dim):
+    """Packed QKV projection + RoPE (GEMM epilogue) + causal GQA attention as one autograd node (sm100 only)."""
+    _need_cuda(x, "qkv_rope_attention")
+    from nanonemo_b200.ops.fused_block import qkv_rope_attention as f
+
+    return f(x, weight, cos, sin, n_heads, n_kv_heads, head_dim)
+
+
+def linear_swiglu(x, weight):
+    """gate||up projection with silu(gate) * up written by the GEMM epilogue (sm100 only)."""
+    _need_cuda(x, "linear_swiglu")
+    from nanonemo_b200.ops.fused_block import linear_swiglu as f
+
+    return f(x, weight)
+
+
 def embedding(idx, weight, impl="torch"):
     if impl == "torch":
         return F.embedding(idx, weight)

@@ -58,6 +58,18 @@ def call(name: str, *args) -> None:
         raise RuntimeError(f"{name} failed (code {rc}): {msg.decode() if msg else 'no message'}")
 
 
+def call_rc(name: str, *args) -> int:
+    """Like `call`, for launchers that answer 1 when they do not serve the problem (nothing was launched): returns 0 or 1."""
+    global LAUNCHES
+    rc = getattr(lib(), name)(*args)
+    if rc == 0:
+        LAUNCHES += 1
+    elif rc != 1:
+        msg = lib().nnb_last_error()
+        raise RuntimeError(f"{name} failed (code {rc}): {msg.decode() if msg else 'no message'}")
+    return rc
+
+
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 

@@ -36,7 +36,9 @@ def fwd_raw(q, k, v, o, scale):
     return lse
 
 
-def bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale):
+def bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale, rope_cos=None, rope_sin=None):
+    """With `rope_cos` / `rope_sin` (fp32 [T, hd / 2], head_dim 64 only) dQ and dK are returned through the inverse RoPE,
+    i.e. as gradients of the projection BEFORE the rotation that produced q and k."""
     B, T, H, hd = q.shape
     KVH = k.shape[2]
     # delta = rowsum(dO * O) is computed inside the launcher's pre-pass kernel
@@ -48,7 +50,7 @@ def bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale):
               *(_lib.i64(s) for s in _strides_bthd(k)), *(_lib.i64(s) for s in _strides_bthd(v)),
               *(_lib.i64(s) for s in _strides_bthd(o)), *(_lib.i64(s) for s in _strides_bthd(do)),
               *(_lib.i64(s) for s in _strides_bthd(dq)), *(_lib.i64(s) for s in _strides_bthd(dk)),
-              *(_lib.i64(s) for s in _strides_bthd(dv)), _lib.f32(scale), _lib.i32(1),
+              *(_lib.i64(s) for s in _strides_bthd(dv)), _lib.f32(scale), _lib.i32(1), _lib.ptr(rope_cos), _lib.ptr(rope_sin),
               _lib.ptr(status_tensor(q.device)), _lib.vp(_lib.stream_ptr()))
 
 

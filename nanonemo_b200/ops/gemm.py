@@ -72,6 +72,53 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def _fused_call(name: str, *args) -> bool:
+    """Launch a GEMM with a fused epilogue; False when the CTA-pair kernel does not serve the shape (the caller then runs
+    the plain GEMM followed by the stand-alone elementwise kernel)."""
+    return _lib.call_rc(name, *args) == 0
+
+
+def gemm_swiglu(x2: torch.Tensor, w_gu: torch.Tensor):
+    """x2 [M, K] @ w_gu [2F, K]^T with the SwiGLU activation in the epilogue -> (gu [M, 2F], act [M, F]) or None."""
+    M, K = x2.shape
+    F = w_gu.shape[0] // 2
+    if M < 256 or F % 128 or w_gu.stride(1) != 1 or x2.stride(1) != 1:
+        return None
+    gu = torch.empty((M, 2 * F), dtype=x2.dtype, device=x2.device)
+    act = torch.empty((M, F), dtype=x2.dtype, device=x2.device)
+    ok = _fused_call("nnb_gemm_swiglu", _lib.ptr(x2), _lib.ptr(w_gu), _lib.ptr(gu), _lib.ptr(act), _lib.i32(M), _lib.i32(F),
+                     _lib.i32(K), _lib.i64(x2.stride(0)), _lib.i64(w_gu.stride(0)), _lib.i64(2 * F), _lib.i64(F),
+                     _lib.i32(_CODE[x2.dtype]), _lib.ptr(status_tensor(x2.device)), _lib.vp(_lib.stream_ptr()))
+    return (gu, act) if ok else None
+
+
+def gemm_rope(x2: torch.Tensor, w: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, t_len: int, rope_cols: int, head_dim: int):
+    """x2 [M, K] @ w [N, K]^T with rotate-half RoPE on columns [0, rope_cols) in the epilogue (row m at position
+    m % t_len; cos / sin fp32 [t_len, head_dim / 2] contiguous) -> [M, N] or None."""
+    M, K = x2.shape
+    N = w.shape[0]
+    if M < 256 or N < 128 or head_dim not in (64, 128) or N % head_dim or rope_cols % head_dim:
+        return None
+    out = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
+    ok = _fused_call("nnb_gemm_rope", _lib.ptr(x2), _lib.ptr(w), _lib.ptr(out), _lib.ptr(cos), _lib.ptr(sin), _lib.i32(M), _lib.i32(N),
+                     _lib.i32(K), _lib.i64(x2.stride(0)), _lib.i64(w.stride(0)), _lib.i64(N), _lib.i32(t_len), _lib.i32(rope_cols),
+                     _lib.i32(head_dim), _lib.i32(_CODE[x2.dtype]), _lib.ptr(status_tensor(x2.device)), _lib.vp(_lib.stream_ptr()))
+    return out if ok else None
+
+
+def gemm_ce_stats(x2: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """out [M, N] = x2 @ w^T plus the per-tile softmax statistics -> stats fp32 [M, ceil(N / 256), 2] or None."""
+    M, K = x2.shape
+    N = w.shape[0]
+    if M < 256 or N < 128 or N % 64:
+        return None
+    stats = torch.empty((M, (N + 255) // 256, 2), dtype=torch.float32, device=x2.device)
+    ok = _fused_call("nnb_gemm_ce_stats", _lib.ptr(x2), _lib.ptr(w), _lib.ptr(out), _lib.ptr(stats), _lib.i32(M), _lib.i32(N),
+                     _lib.i32(K), _lib.i64(x2.stride(0)), _lib.i64(w.stride(0)), _lib.i64(out.stride(0)), _lib.i32(_CODE[x2.dtype]),
+                     _lib.ptr(status_tensor(x2.device)), _lib.vp(_lib.stream_ptr()))
+    return stats if ok else None
+
+
 def compute_dtype() -> torch.dtype:
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
@@ -105,27 +152,36 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
-        w16 = ctx.w16
         dy2 = dy.reshape(-1, dy.shape[-1])
-        if dy2.dtype != x2.dtype:
-            dy2 = dy2.to(x2.dtype)
-        dy2 = _rowmajor2d(dy2)
-        dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w16, b_mn=True)  # [M, K_in]
+        dx, dw = linear_backward(dy2, x2, weight, ctx.w16, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        if dx is not None:
             dx = dx.view(*dy.shape[:-1], x2.shape[-1])
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
-        if ctx.needs_input_grad[1]:
-            main = getattr(weight, "_main_grad", None)
-            if main is not None and main.dtype == torch.float32:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
-                cb = getattr(weight, "_grad_ready_cb", None)
-                if cb is not None and not getattr(weight, "_tied_embedding", False):
-                    cb(weight, True)  # a tied head weight is complete only after the embedding backward
-            else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(weight.dtype)
         return dx, dw
+
+
+def linear_backward(dy2, x2, weight, w16, need_dx: bool, need_dw: bool):
+    """The two backward GEMMs of ``y = x2 @ w16^T``: returns (dx [M, K] or None, dW for autograd or None).
+    When the weight has a slot in the flat gradient buffer (``weight._main_grad``) the weight gradient is accumulated
+    there in fp32 by the GEMM epilogue, the strategy is told the gradient is complete (``_grad_ready_cb``) and the
+    returned dW is None."""
+    if dy2.dtype != x2.dtype:
+        dy2 = dy2.to(x2.dtype)
+    dy2 = _rowmajor2d(dy2)
+    dx = dw = None
+    if need_dx:
+        dx = gemm(dy2, w16, b_mn=True)  # [M, K_in]
+    if need_dw:
+        main = getattr(weight, "_main_grad", None)
+        if main is not None and main.dtype == torch.float32:
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
+            cb = getattr(weight, "_grad_ready_cb", None)
+            if cb is not None and not getattr(weight, "_tied_embedding", False):
+                cb(weight, True)  # a tied head weight is complete only after the embedding backward
+        else:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(weight.dtype)
+    return dx, dw
 
 
 def linear_sm100(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

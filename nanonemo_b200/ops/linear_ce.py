@@ -1,7 +1,8 @@
 """Fused linear + cross-entropy over the tied LM head: mean CE of ``x @ W^T`` without the logits.
 
-Row chunks of the flattened hidden states go through: logits chunk (tcgen05 GEMM, bf16) -> one-pass
-in-place CE kernel (loss per row, logits overwritten with ``(softmax - onehot) / N``) -> ``dx`` chunk
+Row chunks of the flattened hidden states go through: logits chunk (tcgen05 GEMM, bf16, whose epilogue
+also reduces every 256-column tile of a row to its (max, sum-exp)) -> one-sweep in-place CE kernel (combines the tile
+statistics, writes the loss per row, overwrites the logits with ``(softmax - onehot) / N``) -> ``dx`` chunk
 and ``dW +=`` (tcgen05 GEMMs, the latter accumulating in fp32). As in the reference operator
 (nanonemo/kernels/triton/linear_ce.py:44-80) the gradients are produced during the forward pass and
 backward only rescales them by the upstream gradient; the chunk is sized for B200 (32768 rows: one
@@ -12,7 +13,7 @@ waves; the reference uses 512-row chunks on 8 GB parts).
 import torch
 
 from nanonemo_b200.ops import _lib
-from nanonemo_b200.ops.gemm import _CODE, compute_dtype, gemm, shadow_of
+from nanonemo_b200.ops.gemm import _CODE, compute_dtype, gemm, gemm_ce_stats, shadow_of
 
 DEFAULT_CHUNK_ROWS = 32768
 
@@ -21,6 +22,17 @@ def ce_inplace(logits: torch.Tensor, targets: torch.Tensor, loss_rows: torch.Ten
     R, V = logits.shape
     _lib.call("nnb_ce_inplace", _lib.ptr(logits), _lib.ptr(targets), _lib.ptr(loss_rows), _lib.i64(R), _lib.i32(V),
               _lib.i64(logits.stride(0)), _lib.f32(grad_scale), _lib.i32(_CODE[logits.dtype]), _lib.vp(_lib.stream_ptr()))
+
+
+def ce_from_stats(logits: torch.Tensor, targets: torch.Tensor, tile_stats: torch.Tensor, loss_rows: torch.Tensor, grad_scale: float):
+    """One-sweep form of `ce_inplace`: `tile_stats` [R, n_tiles, 2] came out of the head GEMM's epilogue (gemm_ce_stats)."""
+    R, V = logits.shape
+    _lib.call("nnb_ce_grad_from_stats", _lib.ptr(logits), _lib.ptr(targets), _lib.ptr(tile_stats), _lib.i32(tile_stats.shape[1]),
+              _lib.ptr(loss_rows), _lib.i64(R), _lib.i32(V), _lib.i64(logits.stride(0)), _lib.f32(grad_scale),
+              _lib.i32(_CODE[logits.dtype]), _lib.vp(_lib.stream_ptr()))
+
+
+FUSE_STATS = True  # head GEMM epilogue produces the softmax statistics (tests switch it off to compare the two routes)
 
 
 def linear_ce_fwd(x16, w16, targets, chunk_rows, dW_out):
@@ -36,8 +48,12 @@ def linear_ce_fwd(x16, w16, targets, chunk_rows, dW_out):
         r1 = min(r0 + chunk_rows, N)
         lg = logits[: r1 - r0]
         xc = x16[r0:r1]
-        gemm(xc, w16, out=lg)
-        ce_inplace(lg, targets[r0:r1], loss_rows[r0:r1], 1.0 / N)
+        stats = gemm_ce_stats(xc, w16, lg) if FUSE_STATS else None
+        if stats is not None:
+            ce_from_stats(lg, targets[r0:r1], stats, loss_rows[r0:r1], 1.0 / N)
+        else:
+            gemm(xc, w16, out=lg)
+            ce_inplace(lg, targets[r0:r1], loss_rows[r0:r1], 1.0 / N)
         gemm(lg, w16, b_mn=True, out=dx[r0:r1], bn=0 if r1 - r0 >= 16384 else 128)
         gemm(lg, xc, a_mn=True, b_mn=True, out=dW_out, accumulate=True)
     return loss_rows.sum(), dx
@@ -67,7 +83,7 @@ class _LinearCE(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main = getattr(weight, "_main_grad", None)
             if main is not None and main.dtype == torch.float32:
-                main.add_(dW * dloss)  # readiness of the tied weight is reported by the embedding backward
+                main.addcmul_(dW, dloss)  # readiness of the tied weight is reported by the embedding backward
             else:
                 gw = (dW * dloss).to(weight.dtype)
         return gx, gw, None, None

@@ -14,7 +14,13 @@ micro-batch) is done here on index ranges of ``FlatParams.grad``:
   ``1 / world`` average and accumulates the squared norm of the reduced slice for clipping;
   otherwise it is ``dist.all_reduce`` (NCCL, or gloo on CPU) followed by the average;
 * buckets are always launched in bucket order on every rank, so ranks never disagree on the order
-  of collectives.
+  of collectives;
+* the fused kernel keeps its epoch counters in device memory, so with ``cuda_graph: true`` the hooks'
+  launches are captured together with forward and backward and the whole micro-batch, collectives
+  included, replays as one graph;
+* the squared norm of the reduced gradient comes out of the all-reduce kernels themselves (a table of
+  per-block partial sums that every rank adds up in the same order), so clipping costs no pass over
+  the gradient and every rank computes bit-identical clip coefficients.
 
 Gradients are always views into the bucket buffer, which is what ``ddp_grad_as_bucket_view``
 asks for in the reference; the knob is accepted and has no further effect.
@@ -69,7 +75,7 @@ class DDPStrategy(LocalStrategy):
         self.fused = symm is not None
         self._cuda = store.device.type == "cuda"
         self._comm_stream = torch.cuda.Stream(device=store.device) if self._cuda else None
-        self._sumsq = None
+        self._done = False  # finish_grads() already ran for the current step
         for p in store.params:
             p.register_post_accumulate_grad_hook(self._on_grad)
             p._grad_ready_cb = self._on_grad
@@ -91,6 +97,7 @@ class DDPStrategy(LocalStrategy):
             b.pending, b.work = len(b.params), None
         self._next = 0
         self._ready = [False] * len(self.buckets)
+        self._done = False
 
     @contextmanager
     def _no_sync(self):
@@ -127,7 +134,7 @@ class DDPStrategy(LocalStrategy):
             ev.record()
             self._comm_stream.wait_event(ev)
             with torch.cuda.stream(self._comm_stream):
-                self.symm.all_reduce_(b.lo, b.hi, scale=1.0 / self.dp_world)
+                self.symm.all_reduce_(b.lo, b.hi, scale=1.0 / self.dp_world, bucket=self.buckets.index(b))
             self.launches += 1
             b.work = True
         elif self._cuda:
@@ -142,6 +149,8 @@ class DDPStrategy(LocalStrategy):
             b.work = dist.all_reduce(view, group=self.group, async_op=True)
 
     def finish_grads(self):
+        if self._done:
+            return
         # Any bucket whose parameters never produced a gradient this step is still reduced (zeros).
         while self._next < len(self.buckets):
             self._launch(self.buckets[self._next])
@@ -154,7 +163,23 @@ class DDPStrategy(LocalStrategy):
                     b.work.wait()
                 self.store.grad[b.lo:b.hi].mul_(1.0 / self.dp_world)
         self._reset()
+        self._done = True
+
+    def after_graph_replay(self):
+        self._done = True  # the replayed graph contained every bucket's all-reduce and the join of the side stream
 
     def global_sumsq(self):
-        # Every rank holds the same averaged gradient after the all-reduce: the local sum is global.
+        # Every rank holds the same averaged gradient after the all-reduce. The fused kernels left the squared norm of every
+        # reduced slice in a table that is identical on all ranks; otherwise one local pass over the gradient gives it.
+        if self.fused:
+            return self.symm.norm_sq(len(self.buckets))
         return self.store.grad_sumsq()
+
+    def status_words(self) -> list:
+        words = super().status_words()
+        if self.fused:
+            words.append(self.symm.status)
+        return words
+
+    def status_owners(self) -> list:
+        return [self.symm] if self.fused else []

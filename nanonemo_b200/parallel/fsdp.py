@@ -283,6 +283,24 @@ class FSDPStrategy(LocalStrategy):
         dist.all_reduce(sumsq, group=self.group)
         return sumsq
 
+    def status_words(self) -> list:
+        if not self.cuda:
+            return []
+        from nanonemo_b200.ops import _lib
+        from nanonemo_b200.ops.gemm import status_tensor
+
+        words = [status_tensor(self.device)] if _lib.available() else []
+        if self.fused:
+            words.append(self.comm.status)
+        ft = getattr(getattr(self, "tp", None), "fused_tp", None)  # 2-D mesh: the tensor-parallel group's fused linears
+        if ft is not None:
+            words.append(ft.fg.comm_status)
+        return words
+
+    def status_owners(self) -> list:
+        ft = getattr(getattr(self, "tp", None), "fused_tp", None)
+        return ([self.comm] if self.fused else []) + ([ft.fg] if ft is not None else [])
+
     def step(self, opt, grad_clip, scaler=None, keep_grads=False):
         assert scaler is None, "the sharded strategies run in bf16 / fp32 (no loss scaler)"
         if not hasattr(self, "_opt"):

@@ -32,40 +32,86 @@ class LocalStrategy:
     def sync_ctx(self, last: bool):
         return nullcontext()
 
-    def graphed_micro_step(self, x, y, amp_dtype, accum: int):
-        """Forward + backward of one micro-batch replayed from a CUDA graph (single GPU): the whole
-        micro-batch becomes one launch, which is what matters when the batch is small and the step is
-        bound by launch overhead (the reference's ``compile: reduce-overhead`` stage). The first calls
-        run eagerly (warm-up), the next one is captured, later ones copy the batch into the static
-        input buffers and replay. Gradients accumulate into the flat gradient buffer as usual."""
-        st = self.__dict__.setdefault("_graph", {"calls": 0})
-        key = (tuple(x.shape), amp_dtype, accum)
-        if st.get("key") not in (None, key):
-            raise RuntimeError("cuda_graph: the micro-batch shape changed after capture")
+    def graphed_micro_step(self, x, y, amp_dtype, accum: int, last: bool = True):
+        """Forward + backward of one micro-batch replayed from a CUDA graph: the whole micro-batch becomes one launch,
+        which removes the host's enqueue time and most of the gaps between dependent kernels (the reference's
+        ``compile: reduce-overhead`` stage). Under data parallelism the gradient all-reduce kernels of the last
+        micro-batch, launched on the side stream by the gradient-ready hooks, are captured with it and the side stream
+        is joined inside the captured region. The first calls of a (shape, last) pair run eagerly (warm-up), the next
+        one is captured, later ones copy the batch into the static input buffers and replay. Gradients accumulate into
+        the flat gradient buffer as usual."""
+        from nanonemo_b200.ops import _lib
+
+        graphs = self.__dict__.setdefault("_graphs", {})
+        st = graphs.setdefault((tuple(x.shape), amp_dtype, accum, bool(last)), {"calls": 0})
 
         def run(a, b):
-            with torch.autocast("cuda", dtype=amp_dtype, enabled=amp_dtype is not None), self.fwd_ctx():
-                _, loss = self.step_model(a, b)
-            loss = loss / accum
-            loss.backward()
+            with self.sync_ctx(last), self.loss_ctx():
+                with torch.autocast("cuda", dtype=amp_dtype, enabled=amp_dtype is not None), self.fwd_ctx():
+                    _, loss = self.step_model(a, b)
+                loss = loss / accum
+                loss.backward()
+            if last:
+                self.finish_grads()  # joins the collectives' stream: part of the graph when capturing
             return loss.detach()
 
         if "graph" in st:
             st["x"].copy_(x)
             st["y"].copy_(y)
             st["graph"].replay()
+            _lib.LAUNCHES += st["launches"]  # the captured kernels run again without passing through the launch counter
+            self.launches += st["own_launches"]
+            if last:
+                self.after_graph_replay()
             return st["loss"]
         st["calls"] += 1
         if st["calls"] <= 2:  # eager warm-up: allocator, kernel attributes, status buffers
             return run(x, y)
-        st["key"], st["x"], st["y"] = key, x.clone(), y.clone()
+        st["x"], st["y"] = x.clone(), y.clone()
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        n0, own0 = _lib.LAUNCHES, self.launches
         with torch.cuda.graph(graph):
             st["loss"] = run(st["x"], st["y"])
+        st["launches"], st["own_launches"] = _lib.LAUNCHES - n0, self.launches - own0
         st["graph"] = graph
         graph.replay()  # capturing records the work without running it: run this micro-batch now
+        if last:
+            self.after_graph_replay()
         return st["loss"]
+
+    def after_graph_replay(self):
+        """Host-side bookkeeping that the hooks would have done had the micro-batch run eagerly."""
+
+    def status_words(self) -> list:
+        """Device int32 tensors whose FIRST element turns non-zero when a kernel launched on behalf of this strategy gave
+        up on a bounded wait (tensor-core pipelines: ops.gemm.status_tensor; collectives: the communicators' status)."""
+        if self.store is None or self.store.device.type != "cuda":
+            return []
+        from nanonemo_b200.ops import _lib
+        from nanonemo_b200.ops.gemm import status_tensor
+
+        return [status_tensor(self.store.device)] if _lib.available() else []
+
+    def status_flag(self):
+        """0-dim float tensor, non-zero when any status word is set; None when there is nothing to watch. The trainer
+        stacks it with the loss so that it travels in the step's one device -> host copy."""
+        words = self.status_words()
+        if not words:
+            return None
+        return torch.stack([w[0] for w in words]).ne(0).sum().float()
+
+    def raise_on_status(self):
+        """Called once the host has seen a non-zero status flag: raises with the details the kernels recorded."""
+        from nanonemo_b200.ops.gemm import check_status
+
+        for obj in self.status_owners():
+            obj.check_status()
+        check_status()
+        raise RuntimeError("a kernel reported a bounded wait that ran out (status flag set)")
+
+    def status_owners(self) -> list:
+        return []
 
     def full_loss(self, loss: torch.Tensor) -> torch.Tensor:
         return loss

@@ -4,8 +4,9 @@
 the cuMem handles and gives each rank the peers' device pointers, and the NVLS multicast address
 when the driver exposes one). The data movement is this framework's own kernels (csrc/comm.cu):
 peer loads and stores issued from inside the kernel, synchronised by epoch-numbered flags in a
-second symmetric buffer with system-scope release/acquire, every wait bounded (on expiry the kernel
-records {code, rank, peer, block} in a status word and returns; ``check_status`` raises on the host).
+second symmetric buffer with system-scope release/acquire, every wait bounded in time (on expiry the
+kernel records {code, rank, peer, block} in a status word and returns; the training step reads that word
+together with its loss and raises on the host, see ``parallel.strategy.LocalStrategy.status_words``).
 
 The reference has no counterpart: its collectives are NCCL calls made by torch DDP / FSDP2 / DTensor
 (nanonemo/distributed/*.py).
@@ -46,34 +47,69 @@ class SymmetricBuffer:
         self.ptr_array = (ctypes.c_void_p * 16)(*self.peer_ptrs)
 
 
+MAX_NORM_BUCKETS = 256  # rows of the partial-norm table (gradient buckets per optimizer step)
+
+
+def comm_timeout_s() -> float:
+    """Time limit of every cross-GPU wait inside the collective kernels (seconds; NANONEMO_COMM_TIMEOUT_S, default 30)."""
+    return float(os.environ.get("NANONEMO_COMM_TIMEOUT_S", "30"))
+
+
 class SymmetricComm:
-    """Launcher of the collective kernels (csrc/comm.cu) for one group: owns the symmetric flag
-    buffer, the epoch counter and the status words the kernels write when a bounded wait runs out."""
+    """Launcher of the collective kernels (csrc/comm.cu) for one group: owns the symmetric flag buffer, the per-block
+    epoch counters (device memory: the launch arguments never change, so the collectives replay from a CUDA graph) and
+    the status words the kernels write when a bounded wait runs out."""
 
     def __init__(self, device, group, rank: int, world: int, blocks: int | None = None):
         from nanonemo_b200.ops import _lib
 
         self.rank, self.world, self.group = rank, world, group
-        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", "48"))
+        # one block per SM: 256-thread, <= 85-register blocks that share an SM with whatever compute kernel is resident
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", str(sms)))
         words = _lib.lib().nnb_comm_flag_words(self.blocks)
         self.flags = SymmetricBuffer(words, torch.int32, device, group)
         self.flags.tensor.zero_()
+        self.epochs = torch.zeros(self.blocks, dtype=torch.int32, device=device)
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
-        self.epoch = 0
+        self.timeout_s = comm_timeout_s()
+        self.norm_parts = None  # SymmetricBuffer [MAX_NORM_BUCKETS, world, blocks] once enable_norm_parts() was called
+        self._norm_out = None
+        self._null_ptrs = (ctypes.c_void_p * 16)()
         torch.cuda.synchronize(device)
         dist.barrier(group)
 
-    def _next(self):
-        self.epoch += 1
-        return self.epoch
+    def enable_norm_parts(self):
+        """Allocate the table the all-reduce kernels fill with the squared norm of every reduced slice."""
+        dev = self.flags.tensor.device
+        self.norm_parts = SymmetricBuffer(MAX_NORM_BUCKETS * self.world * self.blocks, torch.float32, dev, self.group)
+        self.norm_parts.tensor.zero_()
+        self._norm_out = torch.zeros(1, dtype=torch.float32, device=dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)
 
-    def all_reduce_(self, data: "SymmetricBuffer", lo: int, hi: int, scale: float, multimem: bool = False):
+    def all_reduce_(self, data: "SymmetricBuffer", lo: int, hi: int, scale: float, multimem: bool = False, bucket: int = -1):
+        """In place: data[lo:hi] = scale * sum over ranks. With `bucket` >= 0 (and enable_norm_parts()) the kernel also
+        leaves the squared norm of every reduced slice in row `bucket` of the partial-norm table of every rank."""
         from nanonemo_b200.ops import _lib
 
+        with_norm = bucket >= 0 and self.norm_parts is not None
+        assert bucket < MAX_NORM_BUCKETS
         _lib.call("nnb_allreduce_f32", data.ptr_array, self.flags.ptr_array,
-                  ctypes.c_void_p(data.multicast_ptr if multimem else 0), _lib.ptr(self.status), _lib.i32(self.rank),
-                  _lib.i32(self.world), _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale), _lib.i32(self._next()),
-                  _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+                  self.norm_parts.ptr_array if with_norm else self._null_ptrs,
+                  ctypes.c_void_p(data.multicast_ptr if multimem else 0), _lib.ptr(self.status), _lib.ptr(self.epochs),
+                  _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale),
+                  _lib.i32(max(bucket, 0)), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
+                  ctypes.c_void_p(_lib.stream_ptr()))
+
+    def norm_sq(self, n_buckets: int) -> torch.Tensor:
+        """Sum of the partial-norm rows [0, n_buckets): the squared global norm of the reduced gradient, added in a
+        fixed order (every rank holds the same table, so every rank gets the same bits). 0-dim device tensor."""
+        from nanonemo_b200.ops import _lib
+
+        _lib.call("nnb_sumsq_combine", _lib.ptr(self.norm_parts.tensor), _lib.i64(n_buckets * self.world * self.blocks),
+                  _lib.ptr(self._norm_out), ctypes.c_void_p(_lib.stream_ptr()))
+        return self._norm_out[0]
 
     def reduce_scatter(self, data: "SymmetricBuffer", out: torch.Tensor, sumsq: torch.Tensor | None, lo: int, per: int,
                        scale: float):
@@ -81,16 +117,18 @@ class SymmetricComm:
         from nanonemo_b200.ops import _lib
 
         _lib.call("nnb_reduce_scatter_f32", data.ptr_array, self.flags.ptr_array, _lib.ptr(out), _lib.ptr(sumsq),
-                  _lib.ptr(self.status), _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo), _lib.i64(per),
-                  _lib.f32(scale), _lib.i32(self._next()), _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+                  _lib.ptr(self.status), _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo),
+                  _lib.i64(per), _lib.f32(scale), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
+                  ctypes.c_void_p(_lib.stream_ptr()))
 
     def all_gather(self, shards: "SymmetricBuffer", full: torch.Tensor, src_off_bytes: int, per_bytes: int):
         """full[r * per : (r + 1) * per] = rank r's bytes [src_off, src_off + per) of `shards`."""
         from nanonemo_b200.ops import _lib
 
         _lib.call("nnb_allgather_bytes", shards.ptr_array, self.flags.ptr_array, _lib.ptr(full), _lib.ptr(self.status),
-                  _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(src_off_bytes), _lib.i64(per_bytes),
-                  _lib.i32(self._next()), _lib.i32(self.blocks), ctypes.c_void_p(_lib.stream_ptr()))
+                  _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(src_off_bytes),
+                  _lib.i64(per_bytes), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
+                  ctypes.c_void_p(_lib.stream_ptr()))
 
     def check_status(self):
         st = self.status.tolist()
@@ -101,15 +139,24 @@ class SymmetricComm:
 
 
 class SymmetricAllReduce:
-    """In-place two-shot all-reduce (+ scale) over ranges of one symmetric fp32 buffer."""
+    """In-place two-shot all-reduce (+ scale, + squared norm of the result) over ranges of one symmetric fp32 buffer."""
 
-    def __init__(self, data: SymmetricBuffer, group=None):
+    def __init__(self, data: SymmetricBuffer, group=None, with_norm: bool = True):
         self.data = data
         self.comm = SymmetricComm(data.tensor.device, group, data.rank, data.world)
+        if with_norm:
+            self.comm.enable_norm_parts()
         self.use_multimem = bool(data.multicast_ptr) and os.environ.get("NANONEMO_MULTIMEM", "0") == "1"
 
-    def all_reduce_(self, lo: int, hi: int, scale: float):
-        self.comm.all_reduce_(self.data, lo, hi, scale, self.use_multimem)
+    def all_reduce_(self, lo: int, hi: int, scale: float, bucket: int = -1):
+        self.comm.all_reduce_(self.data, lo, hi, scale, self.use_multimem, bucket)
+
+    def norm_sq(self, n_buckets: int) -> torch.Tensor:
+        return self.comm.norm_sq(n_buckets)
+
+    @property
+    def status(self) -> torch.Tensor:
+        return self.comm.status
 
     def check_status(self):
         self.comm.check_status()

@@ -245,6 +245,17 @@ class TPStrategy(LocalStrategy):
             g = p._main_grad if hasattr(p, "_main_grad") else p.grad
             dist.all_reduce(g, group=self.tp.pair_group)
 
+    def status_words(self) -> list:
+        words = super().status_words()
+        ft = self.tp.fused_tp
+        if ft is not None:
+            words.append(ft.fg.comm_status)
+        return words
+
+    def status_owners(self) -> list:
+        ft = self.tp.fused_tp
+        return [ft.fg] if ft is not None else []
+
     def global_sumsq(self):
         total = self.store.grad_sumsq()
         zero = torch.zeros((), device=total.device)

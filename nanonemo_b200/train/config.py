@@ -58,7 +58,7 @@ class TrainConfig:
     tp_size: int | None = None  # tensor-parallel degree for parallel=tp (default: world) / fsdp_tp
     comm: str = "auto"  # auto | fused | nccl
     residual_dtype: str = "fp32"  # dtype of the residual stream on the sm100 path: fp32 | bf16
-    cuda_graph: bool = False  # capture forward+backward+update of one micro-batch in a CUDA graph (single GPU)
+    cuda_graph: bool = False  # replay forward + backward (+ the ddp gradient all-reduce) of a micro-batch from a CUDA graph
 
     def __post_init__(self):
         if self.fp8_recipe not in ("delayed", "current", "mxfp8"):
@@ -69,8 +69,11 @@ class TrainConfig:
             raise ValueError(f"unknown compile mode {self.compile!r}")
         if self.parallel not in PARALLEL:
             raise ValueError(f"unknown parallel {self.parallel!r}")
-        if self.parallel != "none" and (self.compile == "reduce-overhead" or self.cuda_graph):
-            raise ValueError("CUDA graphs (compile reduce-overhead / cuda_graph) are single-GPU only here")
+        if self.parallel != "none" and self.compile == "reduce-overhead":
+            raise ValueError("compile=reduce-overhead (CUDA graphs of the compiled module) is single-GPU only")
+        if self.cuda_graph and self.parallel not in ("none", "ddp"):
+            raise ValueError("cuda_graph replays the micro-batch on one GPU or under ddp (whose gradient all-reduce kernels "
+                             "are part of the captured graph); fsdp / tp run eagerly")
         if self.fsdp_param_dtype not in ("fp32", "fp16", "bf16"):
             raise ValueError(f"unknown fsdp_param_dtype {self.fsdp_param_dtype!r}")
         if self.fsdp_compile_blocks and (self.parallel != "fsdp" or self.compile is not None):

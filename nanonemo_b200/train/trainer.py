@@ -120,7 +120,10 @@ def _build_parallel(model_cfg: ModelConfig, cfg: TrainConfig, d: parallel.Dist) 
         grad_alloc, finish = make_grad_allreduce(d, cfg.comm)
         store = FlatParams(model, d.device, shadow_dtype(model_cfg, cfg), grad_alloc=grad_alloc,
                            pad_to=256 * d.world * 8)
-        return DDPStrategy(model, d, store, cfg.ddp_bucket_mb, cfg.comm, symm=finish(store), step_model=step_model)
+        strategy = DDPStrategy(model, d, store, cfg.ddp_bucket_mb, cfg.comm, symm=finish(store), step_model=step_model)
+        # the fused all-reduce kernels keep their epochs on the device, so the hooks' launches can be captured
+        strategy.use_cuda_graph = cfg.cuda_graph and strategy.fused and step_model is model
+        return strategy
     if cfg.parallel == "fsdp":
         from nanonemo_b200.parallel.fsdp import build_fsdp
 
@@ -145,15 +148,18 @@ def build_scaler(cfg: TrainConfig, device: str, sharded: bool = False):
 def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, grad_clip: float,
                amp_dtype=None, scaler=None, keep_grads: bool = False, host_sync: bool = True):
     """One optimizer step over `accum` micro-batches -> (mean loss over ranks, pre-clip grad norm),
-    both floats, fetched with a single device->host copy. With host_sync=False the pair is returned
-    as one 2-element device tensor and nothing waits for the GPU."""
+    both floats, fetched with a single device->host copy. The same copy carries the kernels' status
+    flag (non-zero once a bounded wait inside a tensor-core pipeline or a collective ran out): the
+    step raises on every rank that sees it instead of training on with a skipped collective.
+    With host_sync=False the result is returned as one device tensor (loss, norm, status flag) and
+    nothing waits for the GPU; the caller checks element 2 when it reads the tensor."""
     model = strategy.step_model
     loss_sum = None
     for i in range(accum):
         x, y = loader.next_batch()
         torch.compiler.cudagraph_mark_step_begin()  # no-op unless a compiled model replays CUDA graphs
         if getattr(strategy, "use_cuda_graph", False):
-            loss = strategy.graphed_micro_step(x, y, amp_dtype, accum)
+            loss = strategy.full_loss(strategy.graphed_micro_step(x, y, amp_dtype, accum, last=i == accum - 1))
             loss_sum = loss.clone() if loss_sum is None else loss_sum + loss
             continue
         with strategy.sync_ctx(i == accum - 1), strategy.loss_ctx():
@@ -166,11 +172,15 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
         loss_sum = loss if loss_sum is None else loss_sum + loss
     with nvtx.span("optimizer"):
         grad_norm = strategy.step(opt, grad_clip, scaler, keep_grads)
-    both = torch.stack((parallel.all_mean(loss_sum.float()).reshape(()), grad_norm.float().reshape(())))
+    flag = strategy.status_flag()
+    parts = [parallel.all_mean(loss_sum.float()).reshape(()), grad_norm.float().reshape(())]
+    both = torch.stack(parts + [flag.to(parts[0].device)] if flag is not None else parts)
     if not host_sync:
         return both
-    loss_f, norm_f = both.tolist()  # the only host sync of the step
-    return loss_f, norm_f
+    values = both.tolist()  # the only host sync of the step
+    if len(values) > 2 and values[2] != 0:
+        strategy.raise_on_status()
+    return values[0], values[1]
 
 
 def train(model_cfg: ModelConfig, cfg: TrainConfig, device: str | None = None,

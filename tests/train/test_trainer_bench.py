@@ -108,3 +108,29 @@ def test_wandb_mapping():
     out = to_wandb({"step": 3, "loss": 1.0, "lr": 0.1, "tokens_per_s": 5.0, "mfu": 0.3, "event": "x"})
     assert out == {"train/loss": 1.0, "train/lr": 0.1, "perf/tokens_per_s": 5.0, "perf/mfu": 0.3}
     assert to_wandb({"step": 1, "val_loss": 2.0}) == {"val/loss": 2.0}
+
+
+def test_train_step_raises_when_a_kernel_status_word_is_set(tmp_path):
+    """The step's single device -> host read carries the kernels' status flag: a non-zero word (a bounded wait inside a
+    collective or a tensor-core pipeline ran out) makes the step raise instead of training on with skipped work."""
+    from nanonemo_b200 import parallel
+    from nanonemo_b200.data.loader import TokenLoader
+    from nanonemo_b200.train.optim import build_optimizer
+    from nanonemo_b200.train.trainer import build_parallel, train_step
+
+    cfg = TrainConfig(data_dir="synthetic", out_dir=str(tmp_path), seq_len=32, micro_batch=2, global_batch_tokens=64, total_tokens=640)
+    tiny = ModelConfig(n_layers=1, d_model=32, n_heads=2, n_kv_heads=1, d_ff=64, vocab_size=50304, max_seq_len=32)
+    strategy = build_parallel(tiny, cfg, parallel.Dist(device="cpu"))
+    opt = build_optimizer(strategy.model, 1e-3, 0.1, store=strategy.store)
+    loader = TokenLoader("synthetic", "train", 32, 2, device="cpu")
+    loss, norm = train_step(strategy, opt, loader, 1, 1.0)
+    assert loss == loss and norm > 0  # nothing to watch on the CPU: plain (loss, norm)
+    word = torch.zeros(8, dtype=torch.int32)
+    strategy.status_words = lambda: [word]
+    assert len(train_step(strategy, opt, loader, 1, 1.0)) == 2  # a clear word changes nothing
+    out = train_step(strategy, opt, loader, 1, 1.0, host_sync=False)
+    assert out.shape == (3,) and out[2].item() == 0
+    word[0] = 11  # what a collective kernel records when its wait for a peer gives up
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        train_step(strategy, opt, loader, 1, 1.0)
+    assert train_step(strategy, opt, loader, 1, 1.0, host_sync=False)[2].item() == 1
