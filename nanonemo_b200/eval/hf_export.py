@@ -5,7 +5,7 @@ RoPE base 10000, SwiGLU, GQA with query head h on KV head h // group, no biases,
 as in the reference exporter (nanonemo/eval/hf_export.py:22-83). This framework stores the Q/K/V
 projections and the gate/up projections as single fused parameters; the exporter splits them back
 into q/k/v_proj and gate/up_proj. ``load_checkpoint`` reads only the model part of a training
-checkpoint, whatever layout wrote it (they all store full tensors under the same names).
+checkpoint, whatever layout wrote it (they all store the same per-projection names).
 """
 
 import pathlib
@@ -13,7 +13,6 @@ import sys
 from pathlib import Path
 
 import torch
-import torch.distributed.checkpoint as dcp
 
 from nanonemo_b200.models.config import ModelConfig
 from nanonemo_b200.models.model import NanoNemo
@@ -57,14 +56,13 @@ def to_hf(model: NanoNemo):
 
 
 def load_checkpoint(path, cfg: ModelConfig) -> NanoNemo:
-    """Weights of a training checkpoint (the optimizer part is not read) into a CPU model."""
+    """Weights of a training checkpoint (the optimizer part is not read) into a CPU model. Works for checkpoints of this
+    framework and of the reference alike: both store the per-projection names (train/checkpoint.py)."""
+    from nanonemo_b200.train.checkpoint import restore_state
+
     sys.modules.setdefault("pathlib._local", pathlib)  # checkpoints pickled under Python 3.13 name this module
     model = NanoNemo(cfg)
-    state = {"model": {n: p.detach() for n, p in model.named_parameters()}}
-    dcp.load(state, checkpoint_id=str(path))
-    with torch.no_grad():
-        for n, p in model.named_parameters():
-            p.copy_(state["model"][n])
+    restore_state(path, model, None, device="cpu")
     return model.eval()
 
 

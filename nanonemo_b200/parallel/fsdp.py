@@ -19,7 +19,7 @@ norm in the same pass, and the sharded AdamW (one launch for all units) clips wi
 updates the master shard and rewrites the wire shard. Otherwise torch.distributed collectives are
 used (NCCL; on gloo the reduce-scatter is an all-reduce + slice).
 
-Checkpoints gather full tensors (``state_for_checkpoint``) so they load under any layout.
+Checkpoints stream full tensors one unit at a time (``checkpoint_tensors``) so they load under any layout.
 """
 
 from contextlib import nullcontext
@@ -344,35 +344,51 @@ class FSDPStrategy(LocalStrategy):
         self._gather(self.units[0])
         return norm
 
-    # ------------------------------------------------------------------ checkpoint state (full tensors)
-    def _full_from_shards(self, shard_buf):
-        out = {}
+    # ------------------------------------------------------------------ checkpoint state (streamed, one unit at a time)
+    def _state_buffer(self, kind: str) -> torch.Tensor:
+        return {"model": self.shard, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}[kind]
+
+    def checkpoint_names(self) -> list:
+        return [(n, tuple(p.shape)) for u in self.units for n, p in zip(u.names, u.params)]
+
+    def checkpoint_tensors(self, opt, kind: str):
+        """One unit's shards are all-gathered into a transient buffer, its parameters are handed out as views, and the
+        buffer goes away when the consumer moves to the next unit: a save never holds more than one unit unsharded."""
+        buf = self._state_buffer(kind)
         for u in self.units:
             s0, s1 = self._shard_range(u)
-            full = torch.empty(u.hi - u.lo, dtype=shard_buf.dtype, device=self.device)
-            dist.all_gather_into_tensor(full, shard_buf[s0:s1].contiguous(), group=self.group)
+            full = torch.empty(u.hi - u.lo, dtype=buf.dtype, device=self.device)
+            dist.all_gather_into_tensor(full, buf[s0:s1].contiguous(), group=self.group)
             for n, p, o in zip(u.names, u.params, u.offsets):
-                out[n] = full[o:o + p.numel()].view(p.shape).clone()
-        return out
+                yield n, full[o:o + p.numel()].view(p.shape)
 
-    def state_for_checkpoint(self, opt):
-        return {"model": self._full_from_shards(self.shard),
-                "optim": {"exp_avg": self._full_from_shards(self.exp_avg),
-                          "exp_avg_sq": self._full_from_shards(self.exp_avg_sq),
-                          "step": torch.tensor(float(self.opt_step))}}
+    def restore_tensor(self, opt, kind: str, name: str, full: torch.Tensor) -> None:
+        """Parameters arrive in stream order; a unit's slice is written to the shard buffers once all of them are in."""
+        pending = self.__dict__.setdefault("_restore", {})
+        where = self.__dict__.get("_unit_of")
+        if where is None:
+            where = self.__dict__["_unit_of"] = {n: (u, p, o) for u in self.units for n, p, o in zip(u.names, u.params, u.offsets)}
+        u, p, o = where[name]
+        key = (kind, id(u))
+        if key not in pending:
+            pending[key] = [torch.zeros(u.hi - u.lo, dtype=torch.float32, device=self.device), 0]
+        tmp = pending[key]
+        tmp[0][o:o + p.numel()].copy_(full.reshape(-1))
+        tmp[1] += 1
+        if tmp[1] == len(u.params):
+            per = (u.hi - u.lo) // self.world
+            s0, s1 = self._shard_range(u)
+            with torch.no_grad():
+                self._state_buffer(kind)[s0:s1].copy_(tmp[0][self.rank * per:(self.rank + 1) * per])
+            del pending[key]
 
-    def load_from_checkpoint(self, opt, state):
+    def optimizer_step_count(self, opt) -> int:
+        return self.opt_step
+
+    def finish_restore(self, opt, step_count: int) -> None:
+        assert not self.__dict__.get("_restore"), "a unit was only partly restored"
+        self.opt_step = int(step_count)
         with torch.no_grad():
-            for key, buf in (("model", self.shard), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
-                src = state["model"] if key == "model" else state["optim"][key]
-                for u in self.units:
-                    tmp = torch.zeros(u.hi - u.lo, dtype=torch.float32, device=self.device)
-                    for n, p, o in zip(u.names, u.params, u.offsets):
-                        tmp[o:o + p.numel()].copy_(src[n].reshape(-1))
-                    per = (u.hi - u.lo) // self.world
-                    s0, s1 = self._shard_range(u)
-                    buf[s0:s1].copy_(tmp[self.rank * per:(self.rank + 1) * per])
-            self.opt_step = int(float(state["optim"]["step"]))
             self.wire.copy_(self.shard)
         self.gather_all(initial=not self.fused)
 
@@ -420,23 +436,21 @@ class FSDPTPStrategy(FSDPStrategy):
         dist.all_reduce(total)  # over the whole mesh
         return total
 
-    def state_for_checkpoint(self, opt):
+    def checkpoint_names(self) -> list:
+        from nanonemo_b200.parallel.tp import tp_full_shape
+
+        return [(n, tp_full_shape(n, shape, self.tp, self.model.cfg)) for n, shape in super().checkpoint_names()]
+
+    def checkpoint_tensors(self, opt, kind: str):
         from nanonemo_b200.parallel.tp import tp_full_tensor
 
-        st = super().state_for_checkpoint(opt)
-        cfg = self.model.cfg
-        full = lambda d_: {n: tp_full_tensor(n, t, self.tp, cfg) for n, t in d_.items()}
-        return {"model": full(st["model"]), "optim": {"exp_avg": full(st["optim"]["exp_avg"]),
-                                                        "exp_avg_sq": full(st["optim"]["exp_avg_sq"]), "step": st["optim"]["step"]}}
+        for n, local in super().checkpoint_tensors(opt, kind):
+            yield n, tp_full_tensor(n, local, self.tp, self.model.cfg)
 
-    def load_from_checkpoint(self, opt, state):
+    def restore_tensor(self, opt, kind: str, name: str, full: torch.Tensor) -> None:
         from nanonemo_b200.parallel.tp import tp_local_slice
 
-        cfg = self.model.cfg
-        loc = lambda d_: {n: tp_local_slice(n, t, self.tp, cfg) for n, t in d_.items()}
-        super().load_from_checkpoint(opt, {"model": loc(state["model"]),
-                                           "optim": {"exp_avg": loc(state["optim"]["exp_avg"]),
-                                                     "exp_avg_sq": loc(state["optim"]["exp_avg_sq"]), "step": state["optim"]["step"]}})
+        super().restore_tensor(opt, kind, name, tp_local_slice(name, full.to(self.device), self.tp, self.model.cfg))
 
 
 def build_fsdp(model_cfg, cfg, d):

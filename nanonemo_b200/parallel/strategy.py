@@ -162,42 +162,59 @@ class LocalStrategy:
     def scale_grads_(self, coef: torch.Tensor):
         self.store.grad.mul_(coef.to(self.store.grad.dtype))
 
-    # -- checkpoint state: layout-independent, full tensors keyed by parameter name
-    def named_full_params(self):
-        """(name, full fp32 tensor) for every parameter, the tied weight once."""
-        return [(n, p.detach()) for n, p in self.model.named_parameters()]
+    # -- checkpoint state, streamed: one full fp32 tensor at a time under this framework's parameter names.
+    # train/checkpoint.py turns the stream into the on-disk key set and keeps only this rank's row block of every tensor, so
+    # no rank ever holds more than one full tensor beyond its 1 / world share. Every rank walks the stream in the same
+    # order (sharded layouts issue a collective per tensor or per unit).
+    STATE_KINDS = ("model", "exp_avg", "exp_avg_sq")
 
-    def state_for_checkpoint(self, opt) -> dict:
-        """{"model": {name: tensor}, "optim": {"exp_avg": {...}, "exp_avg_sq": {...}, "step": tensor}}.
-        Every strategy produces the same names and FULL shapes, so a checkpoint written under one
-        layout loads under any other."""
-        model, avg, avg_sq = {}, {}, {}
-        step = torch.zeros((), dtype=torch.float32)
-        by_param = {id(p): n for n, p in self.model.named_parameters()}
+    def checkpoint_names(self) -> list:
+        """[(name, full shape)] of every parameter, the tied weight once, in the order the streams use."""
+        return [(n, tuple(p.shape)) for n, p in self.model.named_parameters()]
+
+    def checkpoint_tensors(self, opt, kind: str):
+        """Yields (name, full tensor) for kind in STATE_KINDS; a moment that does not exist yet is zeros."""
         for n, p in self.model.named_parameters():
-            model[n] = p.detach()
-        for p, st in opt.state.items():
-            n = by_param.get(id(p))
-            if n is None or not st:
-                continue
-            avg[n], avg_sq[n] = st["exp_avg"], st["exp_avg_sq"]
-            step = torch.as_tensor(st["step"], dtype=torch.float32).detach().cpu().reshape(())
-        for n, p in self.model.named_parameters():  # a load target exists even before the first step
-            avg.setdefault(n, torch.zeros_like(p))
-            avg_sq.setdefault(n, torch.zeros_like(p))
-        return {"model": model, "optim": {"exp_avg": avg, "exp_avg_sq": avg_sq, "step": step}}
+            if kind == "model":
+                yield n, p.detach()
+            else:
+                st = opt.state.get(p, {}) if opt is not None else {}
+                yield n, st[kind].detach() if kind in st else torch.zeros_like(p)
 
-    def load_from_checkpoint(self, opt, state: dict) -> None:
-        step = float(state["optim"]["step"])
+    def restore_tensor(self, opt, kind: str, name: str, full: torch.Tensor) -> None:
+        p = self._params_by_name()[name]
         with torch.no_grad():
-            for n, p in self.model.named_parameters():
-                p.copy_(state["model"][n])
-                st = opt.state[p]
-                if "exp_avg" not in st:
-                    st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(p), torch.zeros_like(p)
-                st["exp_avg"].copy_(state["optim"]["exp_avg"][n])
-                st["exp_avg_sq"].copy_(state["optim"]["exp_avg_sq"][n])
-                st["step"] = torch.tensor(step, dtype=torch.float32)
+            if kind == "model":
+                p.copy_(full)
+                return
+            st = opt.state[p]
+            if "exp_avg" not in st:
+                st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(p), torch.zeros_like(p)
+                st["step"] = torch.tensor(0.0, dtype=torch.float32)
+            st[kind].copy_(full)
+
+    def _params_by_name(self) -> dict:
+        cache = self.__dict__.get("_by_name")
+        if cache is None:
+            cache = self.__dict__["_by_name"] = dict(self.model.named_parameters())
+        return cache
+
+    def optimizer_step_count(self, opt) -> int:
+        for st in (opt.state.values() if opt is not None else ()):
+            if "step" in st:
+                return int(float(st["step"]))
+        return 0
+
+    def finish_restore(self, opt, step_count: int) -> None:
+        """After every tensor has been restored: set the optimizer's step counter and refresh whatever is derived from
+        the weights (the 16-bit shadow, the views of the flat buffers)."""
+        if opt is not None:
+            if hasattr(opt, "set_step_count"):
+                opt.set_step_count(step_count)
+            else:
+                for st in opt.state.values():
+                    if "step" in st:
+                        st["step"] = torch.tensor(float(step_count), dtype=torch.float32)
         if self.store is not None:
             self.store.rebind_grads()
             self.store.refresh_shadow()

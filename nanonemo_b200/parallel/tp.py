@@ -271,22 +271,16 @@ class TPStrategy(LocalStrategy):
     def _local(self, name, full):
         return tp_local_slice(name, full, self.tp, self.model.cfg)
 
-    def state_for_checkpoint(self, opt):
-        base = super().state_for_checkpoint(opt)
-        out = {"model": {}, "optim": {"exp_avg": {}, "exp_avg_sq": {}, "step": base["optim"]["step"]}}
-        for n in base["model"]:
-            out["model"][n] = self._full(n, base["model"][n])
-            out["optim"]["exp_avg"][n] = self._full(n, base["optim"]["exp_avg"][n])
-            out["optim"]["exp_avg_sq"][n] = self._full(n, base["optim"]["exp_avg_sq"][n])
-        return out
+    def checkpoint_names(self) -> list:
+        return [(n, tp_full_shape(n, shape, self.tp, self.model.cfg)) for n, shape in super().checkpoint_names()]
 
-    def load_from_checkpoint(self, opt, state):
-        local = {"model": {}, "optim": {"exp_avg": {}, "exp_avg_sq": {}, "step": state["optim"]["step"]}}
-        for n in state["model"]:
-            local["model"][n] = self._local(n, state["model"][n])
-            local["optim"]["exp_avg"][n] = self._local(n, state["optim"]["exp_avg"][n])
-            local["optim"]["exp_avg_sq"][n] = self._local(n, state["optim"]["exp_avg_sq"][n])
-        super().load_from_checkpoint(opt, local)
+    def checkpoint_tensors(self, opt, kind: str):
+        for n, local in super().checkpoint_tensors(opt, kind):
+            yield n, self._full(n, local)
+
+    def restore_tensor(self, opt, kind: str, name: str, full: torch.Tensor) -> None:
+        dev = next(self.model.parameters()).device
+        super().restore_tensor(opt, kind, name, self._local(name, full.to(dev)))
 
 
 def is_attention_weight(name: str) -> bool:
@@ -310,6 +304,18 @@ def tp_full_tensor(name, local, tp, cfg):
         f = cfg.d_ff // W
         return torch.cat([p[:f] for p in parts] + [p[f:] for p in parts])
     return torch.cat(parts, dim=rule)
+
+
+def tp_full_shape(name, local_shape, tp, cfg) -> tuple:
+    """Shape of the full tensor whose tensor-parallel shard has `local_shape`."""
+    rule = shard_rule(name)
+    if rule is None:
+        return tuple(local_shape)
+    W = tp.attn_world if is_attention_weight(name) else tp.world
+    dim = 0 if rule in ("qkv", "gu") else rule
+    full = list(local_shape)
+    full[dim] *= W
+    return tuple(full)
 
 
 def tp_local_slice(name, full, tp, cfg):

@@ -39,6 +39,21 @@ class FusedAdamW(torch.optim.AdamW):
         self._n_steps = 0
         if store is not None:
             store.attach_optimizer(self)
+            if store.fused_ok:
+                self.set_step_count(0)
+
+    def set_step_count(self, n: int) -> None:
+        """Every parameter's ``step`` entry becomes ONE shared CPU scalar on the fused path (the kernel updates all
+        parameters in the same launch, so there is one counter to advance per step, not one per parameter)."""
+        self._n_steps = int(n)
+        if self.store is not None and self.store.fused_ok:
+            shared = torch.tensor(float(n), dtype=torch.float32)
+            for st in self.state.values():
+                st["step"] = shared
+            self._shared_step = shared
+        else:
+            for st in self.state.values():
+                st["step"] = torch.tensor(float(n), dtype=torch.float32)
 
     @torch.no_grad()
     def step(self, closure=None, grad_norm_sq: torch.Tensor | None = None, max_norm: float | None = None):
@@ -47,10 +62,14 @@ class FusedAdamW(torch.optim.AdamW):
         if store is None or not store.fused_ok:
             assert grad_norm_sq is None, "clip-in-update needs the flat fused path"
             return super().step(closure)
-        self._n_steps = int(next(iter(self.state.values()))["step"].item()) + 1 if self.state else 1
+        shared = getattr(self, "_shared_step", None)
+        first = next(iter(self.state.values()))["step"] if self.state else None
+        if shared is None or first is not shared:  # state was replaced from outside (load_state_dict): re-share it
+            self.set_step_count(int(float(first)) if first is not None else 0)
+            shared = self._shared_step
+        self._n_steps = int(float(shared)) + 1
         store.fused_adamw_step(self, self._n_steps, grad_norm_sq, max_norm)
-        for st in self.state.values():
-            st["step"].fill_(self._n_steps)
+        shared.fill_(self._n_steps)
         return None
 
 

@@ -1,5 +1,6 @@
-"""Two real GPUs: every layout on the sm100 kernels with the fused NVLink collectives must track the
-single-GPU losses (bf16, tolerance 2e-2), through the real CLI under torch.distributed.run."""
+"""Real GPUs: every layout on the sm100 kernels with the fused NVLink collectives must track the single-GPU losses (bf16,
+tolerance 2e-2). Two GPUs go through the real CLI under torch.distributed.run, layout by layout; 2, 4 and 8 GPUs run
+``parity_worker.py`` once per world size (exact checks of the collective kernels, then all layouts in one process group)."""
 
 import json
 import os
@@ -50,3 +51,19 @@ def test_two_gpus_track_one_gpu(tmp_path, par, extra, loss, embed):
     multi = run(tmp_path, "two", 2, f"train.parallel={par}", *extra, loss=loss, embed=embed)
     assert len(single) == len(multi) == 8
     assert multi == pytest.approx(single, abs=2e-2), (single, multi)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_layouts_and_collectives_at_world_size(world):
+    """Exact all-reduce / reduce-scatter / all-gather values and in-kernel gradient norm at this world size, then ddp, ddp replayed
+    from a CUDA graph, fsdp, tp (rank pairs at 8: 4 KV heads) and the fsdp x tp mesh against a single-GPU run."""
+    import torch
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+                        "127.0.0.1", "--master-port", str(29580 + world), str(ROOT / "tests" / "distributed" / "parity_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=900)
+    print(r.stdout[-4000:])
+    assert r.returncode == 0 and "PARITY_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -155,3 +155,12 @@ def test_attention_layout_and_pair_slices_without_processes():
     # the MLP stays split 8 ways
     full_down = torch.arange(D * cfg.d_ff, dtype=torch.float32).view(D, cfg.d_ff)
     assert tp_local_slice("blocks.0.mlp.w_down.weight", full_down, ranks[3], cfg).shape == (D, cfg.d_ff // 8)
+
+
+def test_each_rank_saves_its_share_only():
+    """A checkpoint save hands DCP 1 / world of the state per rank under every layout (row blocks as DTensor shards)."""
+    env = dict(os.environ, NANONEMO_DEVICE="cpu", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29549", str(ROOT / "tests" / "distributed" / "ckpt_share_worker.py")],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "SHARE_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
