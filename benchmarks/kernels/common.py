@@ -1,10 +1,11 @@
 """Timing harness for kernel micro-benchmarks on B200.
 
-Each measurement: warm-up calls, then `iters` timed calls; before every timed call a buffer larger
-than the L2 cache is overwritten so the kernel starts cold (the size comes from the device's L2
-attribute — 126 MB on B200, so the reference's fixed 64 MB flush, benchmarks/kernels/common.py:42,
-would not be enough); CUDA events on the launching stream bracket the call; the median is
-reported. Clock samples are taken during the run and the result carries the compact clocks record.
+Each measurement: warm-up calls, the call captured into a CUDA graph, then `iters` timed replays; before
+every replay a buffer larger than the L2 cache is overwritten so the kernel starts cold (the size comes
+from the device's L2 attribute — 126 MB on B200, so the reference's fixed 64 MB flush,
+benchmarks/kernels/common.py:42, would not be enough); CUDA events on the launching stream bracket the
+replay, the host synchronises once at the end, and the median is reported (the reference harness times
+graph replays for the same reason, benchmarks/kernels/common.py:30-64). Clock samples are taken during the run and the result carries the compact clocks record.
 Bandwidth figures are computed against the MINIMUM bytes the operator must move.
 """
 
@@ -31,20 +32,51 @@ def l2_flush():
     _flush.zero_()
 
 
-def time_ms(fn, iters: int = 30, warmup: int = 5, flush: bool = True) -> float:
-    for _ in range(warmup):
-        fn()
+def _captured(fn, warmup: int):
+    """`fn` recorded into a CUDA graph (after warm-up on a side stream, as capture requires), or None when the call cannot
+    be captured (it synchronises, or allocates outside the graph's pool)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    times = []
-    for _ in range(iters):
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(graph):
+            fn()
+    except Exception as e:  # noqa: BLE001 - fall back to timing plain launches
+        print(f"[time_ms] not capturable, timing plain launches instead: {type(e).__name__}: {str(e)[:200]}", file=sys.stderr)
+        torch.cuda.synchronize()
+        return None
+    return graph
+
+
+def time_ms(fn, iters: int = 30, warmup: int = 5, flush: bool = True, graph: bool = True, spread: bool = False):
+    """Median device time of one call of `fn` in ms. By default the call is captured into a CUDA graph once and every timed
+    repetition is flush -> event -> graph replay -> event with a single synchronize at the end, so neither the host's launch
+    overhead nor its jitter lands between the two events (a 40 us kernel timed around a Python-level launch carries a few
+    us of noise). `graph=False` times plain launches. `spread=True` returns {"median", "p20", "p80"} instead."""
+    replay = _captured(fn, warmup) if graph else None
+    call = replay.replay if replay is not None else fn
+    if replay is None:
+        for _ in range(warmup):
+            fn()
+    for _ in range(3):
+        call()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for first, second in pairs:
         if flush:
             l2_flush()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        first.record()
+        call()
+        second.record()
+    torch.cuda.synchronize()
+    times = sorted(a.elapsed_time(b) for a, b in pairs)
+    if spread:
+        pick = lambda q: times[min(len(times) - 1, int(q * len(times)))]
+        return {"median": median(times), "p20": pick(0.2), "p80": pick(0.8)}
     return median(times)
 
 

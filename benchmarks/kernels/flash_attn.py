@@ -1,7 +1,12 @@
-"""Causal GQA attention: the tcgen05 kernels vs PyTorch SDPA (mem-efficient = the reference's choice; flash
-and cuDNN for context) at the training shape B=32, H=12, KVH=4, T=1024, hd=64 and a few others.
+"""Causal GQA attention: the tcgen05 kernels vs PyTorch SDPA (mem-efficient = the reference's choice; the default backend
+and flash for context) at the training shape B=32, H=12, KVH=4, T=1024, hd=64 and a few others.
 
     python benchmarks/kernels/flash_attn.py [--quick]
+
+Columns: forward alone, forward + backward through autograd (what a training step pays, repeat_interleave of K / V included
+for the SDPA providers, which have no GQA-direct path on every backend), and the BACKWARD alone (the gradient call on a
+retained graph: for `sm100` that is the delta pre-pass, the backward kernel and the dQ conversion). All timed as CUDA-graph
+replays with the L2 flushed before each.
 """
 
 import argparse
@@ -25,10 +30,13 @@ def flops(B, H, T, hd, bwd):
 def rows_fn(quick):
     rows = []
     for B, H, KVH, T, hd in (CASES[:1] if quick else CASES):
-        q = torch.randn(B, T, H, hd, device="cuda", dtype=torch.bfloat16).transpose(1, 2).requires_grad_()
-        k = torch.randn(B, T, KVH, hd, device="cuda", dtype=torch.bfloat16).transpose(1, 2).requires_grad_()
-        v = torch.randn(B, T, KVH, hd, device="cuda", dtype=torch.bfloat16).transpose(1, 2).requires_grad_()
-        g = torch.randn(B, H, T, hd, device="cuda", dtype=torch.bfloat16)
+        # inputs come from the CPU generator: a provider whose capture into a CUDA graph fails can leave the CUDA generator
+        # unusable for the rest of the process
+        rnd = lambda *shape: torch.randn(*shape).to("cuda", torch.bfloat16)
+        q = rnd(B, T, H, hd).transpose(1, 2).requires_grad_()
+        k = rnd(B, T, KVH, hd).transpose(1, 2).requires_grad_()
+        v = rnd(B, T, KVH, hd).transpose(1, 2).requires_grad_()
+        g = rnd(B, H, T, hd)
 
         def sdpa(backend):
             def f():
@@ -37,17 +45,22 @@ def rows_fn(quick):
                     return F.scaled_dot_product_attention(q, kk, vv, is_causal=True)
             return f
 
+        def sdpa_default():
+            return F.scaled_dot_product_attention(q, k.repeat_interleave(H // KVH, 1), v.repeat_interleave(H // KVH, 1), is_causal=True)
+
         providers = {"sm100": lambda: ops.flash_attn(q, k, v), "sdpa_mem_efficient": sdpa(SDPBackend.EFFICIENT_ATTENTION),
-                     "sdpa_flash": sdpa(SDPBackend.FLASH_ATTENTION)}
+                     "sdpa_flash": sdpa(SDPBackend.FLASH_ATTENTION), "sdpa_default": sdpa_default}
         for name, fn in providers.items():
             try:
                 t_f = time_ms(fn, iters=20)
                 t_fb = time_ms(lambda: torch.autograd.grad(fn(), (q, k, v), g), iters=20)
+                out = fn()
+                t_b = time_ms(lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True), iters=20)
             except Exception as e:  # a backend that does not support the shape
                 rows.append({"case": f"B{B} H{H}/{KVH} T{T} hd{hd}", "provider": name, "fwd_ms": float("nan"), "fwd_bwd_ms": float("nan"),
-                             "fwd_tflops": 0.0, "fwd_bwd_tflops": 0.0, "note": type(e).__name__})
+                             "bwd_ms": float("nan"), "fwd_tflops": 0.0, "fwd_bwd_tflops": 0.0, "note": type(e).__name__})
                 continue
-            rows.append({"case": f"B{B} H{H}/{KVH} T{T} hd{hd}", "provider": name, "fwd_ms": t_f, "fwd_bwd_ms": t_fb,
+            rows.append({"case": f"B{B} H{H}/{KVH} T{T} hd{hd}", "provider": name, "fwd_ms": t_f, "fwd_bwd_ms": t_fb, "bwd_ms": t_b,
                          "fwd_tflops": flops(B, H, T, hd, False) / t_f / 1e9, "fwd_bwd_tflops": flops(B, H, T, hd, True) / t_fb / 1e9,
                          "note": ""})
         check_status()

@@ -48,7 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        extra = os.environ.get("NANONEMO_NVCC_EXTRA", "").split()  # e.g. -DNNB_PROFILE: in-kernel phase timers of the attention kernels
+        cmd = [nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         (objdir / (src.stem + ".ptxas.log")).write_text(r.stderr)
         return src, r

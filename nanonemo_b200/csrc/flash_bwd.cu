@@ -15,8 +15,18 @@
 // staging tile and a TMA reduce-add (cp.reduce.async.bulk.tensor .add.f32) into an fp32 buffer that a
 // small kernel converts at the end. D = rowsum(dO * O) is a pre-pass kernel in this file.
 // 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 compute: two threads per query row,
-// one for keys 0..63 of the tile and one for keys 64..127 (same TMEM lanes, different columns), which
-// halves the latency of the softmax phase the tensor core has to wait for. All waits are bounded.
+// one for keys 0..63 of the tile and one for keys 64..127 (same TMEM lanes, different columns).
+//
+// Software pipeline. The score tile is double buffered in tensor memory (S0 | S1 | dP | dV | dK = 512 columns; the dQ
+// partial product of a visit is accumulated into the first 64 columns of THAT visit's S buffer, which is free once P has
+// been computed from it), and the compute work of a visit is split into  A: P = exp(S scale - L)  /  B: dS = P (dP - D) scale,
+// with the dQ drain of the PREVIOUS visit between them. The tensor core then always has work that does not depend on the
+// phase the compute warps are in:
+//     compute :  A(n)          drain dQ(n-1)     B(n)                    A(n+1)   ...
+//     tensor  :        dV(n)               S(n+1)      dK(n) dQ(n) dP(n+1)
+// S(n+1) is ready long before A(n+1) starts, dP(n+1) before B(n+1), dQ(n) before its drain, so neither side waits for the
+// other in steady state; a visit costs about the compute warps' own work instead of the sum of all phases.
+// All waits are bounded.
 #include <cstdlib>
 #include <type_traits>
 
@@ -30,7 +40,7 @@ constexpr int BQ = 128, BKV = 128, HD = 64;
 constexpr int kThreads = 320;           // TMA warp, MMA warp, 2 x 4 compute warps
 constexpr int kComputeThreads = 256;
 constexpr int kTile16 = 128 * 64 * 2;     // a [128 x 64] 16-bit tile = 16 KB
-constexpr int kStagesQ = 2;
+constexpr int kStagesQ = 3;             // a stage is released when dK / dQ of its visit are done and refilled two visits ahead
 // shared memory map (bytes)
 constexpr int kOffK = 0, kOffV = kTile16, kOffQdO = 2 * kTile16;               // ring of (Q | dO)
 constexpr int kOffP = kOffQdO + kStagesQ * 2 * kTile16, kOffdS = kOffP + 2 * kTile16;
@@ -38,7 +48,8 @@ constexpr int kOffStage = kOffdS + 2 * kTile16;                                /
 constexpr int kOffBars = kOffStage + 2 * kTile16;
 constexpr int kSmem = kOffBars + 256 + 1024;
 // tensor memory columns
-constexpr int kColS = 0, kColdP = 128, kColdV = 256, kColdK = 320, kColdQ = 384, kTmemCols = 512;
+constexpr int kColS = 0 /* two buffers: + 128 * (visit & 1) */, kColdP = 256, kColdV = 384, kColdK = 448, kTmemCols = 512;
+constexpr int kColdQ = kColS;            // dQ(n) lands in columns [0, 64) of S buffer (n & 1), after P(n) has been taken from it
 
 struct BParams {
   int B, H, KVH, T, n_q_tiles, group;
@@ -63,15 +74,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
-  // barriers: kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full, dq_read
-  const uint32_t bar_kv = smem_u32(bars), bar_qf = bar_kv + 8, bar_qe = bar_qf + 16;
-  const uint32_t bar_sdp = bar_qe + 16, bar_pds = bar_sdp + 8, bar_dq = bar_pds + 8, bar_dqr = bar_dq + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  // barriers: kv_full, q_full[3], q_empty[3], s_full[2], dp_full, p_written, ds_written, dq_full, dq_read
+  const uint32_t bar_kv = smem_u32(bars), bar_qf = bar_kv + 8, bar_qe = bar_qf + 8 * kStagesQ;
+  const uint32_t bar_s = bar_qe + 8 * kStagesQ, bar_dp = bar_s + 16, bar_p = bar_dp + 8, bar_ds = bar_p + 8;
+  const uint32_t bar_dq = bar_ds + 8, bar_dqr = bar_dq + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 2 * kStagesQ + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;          // key tile
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // Longest-job-first over the whole grid: key tile 0 is visited by every query tile, the last one by a single tile, and the
+  // key tile is the slowest-varying block index, so the heavy CTAs all start first and the kernel ends on the short ones.
+  const int kt = blockIdx.z;          // key tile
+  const int kvh = blockIdx.x, b = blockIdx.y;
   const int first_qt = (kt * BKV) / BQ;                     // first query tile that can see these keys
   const int n_qt = p.n_q_tiles - first_qt;                  // query tiles per head of the group
   const int iters = n_qt * p.group;
@@ -82,8 +96,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar_qf + 8 * s, 1);
       mbar_init(bar_qe + 8 * s, 1);
     }
-    mbar_init(bar_sdp, 1);
-    mbar_init(bar_pds, kComputeThreads);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_s + 8, 1);
+    mbar_init(bar_dp, 1);
+    mbar_init(bar_p, kComputeThreads);
+    mbar_init(bar_ds, kComputeThreads);
     mbar_init(bar_dq, 1);
     mbar_init(bar_dqr, kComputeThreads);
     *abort_flag = 0;
@@ -120,49 +137,67 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
-      if (!ok) fail_role = 2;
       const uint32_t sK = s_base + kOffK, sV = s_base + kOffV, sP = s_base + kOffP, sdS = s_base + kOffdS;
-      // S = Q K^T and dP = dO V^T for visit n: all operands K-major, 4 k-steps of 16 over head_dim
-      auto issue_sdp = [&](int n) -> bool {
-        const uint32_t s = n % kStagesQ, ph = (n / kStagesQ) & 1;
-        const uint32_t sQ = s_base + kOffQdO + s * 2 * kTile16, sdO = sQ + kTile16;
-        if (!mbar_wait(bar_qf + 8 * s, ph, abort_flag)) return false;
-        tc_fence_after();
+      auto stage_of = [&](int n) { return s_base + kOffQdO + (uint32_t)(n % kStagesQ) * 2 * kTile16; };
+      auto wait_q = [&](int n) { return mbar_wait(bar_qf + 8 * (n % kStagesQ), (n / kStagesQ) & 1, abort_flag); };
+      // S(n) = Q K^T into score buffer n & 1 (K-major operands, 4 k-steps of 16 over head_dim)
+      auto issue_s = [&](int n) {
+        const uint32_t sQ = stage_of(n);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          umma_f16(tmem_base + kColS, make_smem_desc(sQ + k * 32, 16, 1024), make_smem_desc(sK + k * 32, 16, 1024), p.idesc_s, k > 0);
+          umma_f16(tmem_base + kColS + (n & 1) * BKV, make_smem_desc(sQ + k * 32, 16, 1024), make_smem_desc(sK + k * 32, 16, 1024), p.idesc_s, k > 0);
+        umma_commit(bar_s + 8 * (n & 1));
+      };
+      // dP(n) = dO V^T
+      auto issue_dp = [&](int n) {
+        const uint32_t sdO = stage_of(n) + kTile16;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           umma_f16(tmem_base + kColdP, make_smem_desc(sdO + k * 32, 16, 1024), make_smem_desc(sV + k * 32, 16, 1024), p.idesc_s, k > 0);
-        umma_commit(bar_sdp);
-        return true;
+        umma_commit(bar_dp);
       };
-      if (ok && iters > 0) ok = issue_sdp(0);
+      if (ok && iters > 0) {
+        ok = wait_q(0);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+          issue_dp(0);
+        }
+      }
       for (int n = 0; n < iters && ok; ++n) {
-        const uint32_t s = n % kStagesQ;
-        const uint32_t sQ = s_base + kOffQdO + s * 2 * kTile16, sdO = sQ + kTile16;
-        if (!mbar_wait(bar_pds, n & 1, abort_flag)) { ok = false; break; }   // P, dS written; S, dP consumed
-        if (n > 0 && !mbar_wait(bar_dqr, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        const uint32_t sQ = stage_of(n), sdO = sQ + kTile16;
+        if (!mbar_wait(bar_p, n & 1, abort_flag)) { ok = false; break; }     // P(n) is in shared memory, S(n) has been read
         tc_fence_after();
-        // dV += P^T dO and dK += dS^T Q: A = [query][key] tile read MN-major (M = keys: two 64-key groups
-        // 16 KB apart), B = [query][hd] tile read MN-major; 8 k-steps of 16 query rows (2048 bytes each).
+        // dV += P^T dO: A = [query][key] tile read MN-major (M = keys: two 64-key groups 16 KB apart), B = [query][hd]
+        // tile read MN-major; 8 k-steps of 16 query rows (2048 bytes each).
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k)
           umma_f16(tmem_base + kColdV, make_smem_desc(sP + k * 2048, kTile16, 1024), make_smem_desc(sdO + k * 2048, kTile16, 1024),
                    p.idesc_dkv, (n > 0 || k > 0) ? 1u : 0u);
+        if (n + 1 < iters) {
+          // S(n + 1) goes into the other score buffer, whose first columns held dQ(n - 1): wait until that was drained.
+          // Its commit also covers dV(n) above, so P may be overwritten as soon as S(n + 1) is seen complete.
+          if (n >= 1 && !mbar_wait(bar_dqr, (n - 1) & 1, abort_flag)) { ok = false; break; }
+          if (!wait_q(n + 1)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(n + 1);
+        }
+        if (!mbar_wait(bar_ds, n & 1, abort_flag)) { ok = false; break; }    // dS(n) is in shared memory, dP(n) has been read
+        tc_fence_after();
+        // dK += dS^T Q (operands as for dV)
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k)
           umma_f16(tmem_base + kColdK, make_smem_desc(sdS + k * 2048, kTile16, 1024), make_smem_desc(sQ + k * 2048, kTile16, 1024),
                    p.idesc_dkv, (n > 0 || k > 0) ? 1u : 0u);
-        // dQ = dS K: A = dS K-major over keys (two 64-key blocks), B = K tile read MN-major (16 key rows per step)
+        // dQ(n) = dS K into the score buffer of this visit: A = dS K-major over keys (two 64-key blocks), B = K tile read
+        // MN-major (16 key rows per step)
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
-          umma_f16(tmem_base + kColdQ, make_smem_desc(sdS + (k / 4) * kTile16 + (k % 4) * 32, 16, 1024),
+          umma_f16(tmem_base + kColdQ + (n & 1) * BKV, make_smem_desc(sdS + (k / 4) * kTile16 + (k % 4) * 32, 16, 1024),
                    make_smem_desc(sK + k * 2048, kTile16, 1024), p.idesc_dq, k > 0);
         umma_commit(bar_dq);
-        umma_commit(bar_qe + 8 * s);
-        // the score tiles of the NEXT visit run on the tensor core while the compute warps drain dQ of this one
-        if (n + 1 < iters) ok = issue_sdp(n + 1);
+        umma_commit(bar_qe + 8 * (n % kStagesQ));
+        if (n + 1 < iters) issue_dp(n + 1);   // dP(n) was consumed (bar_ds), Q / dO of visit n + 1 were awaited above
       }
       if (!ok) fail_role = 2;
     }
@@ -179,72 +214,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
     NNB_PROF_DECL;
     constexpr float kLog2e = 1.4426950408889634f;
-    for (int n = 0; n < iters; ++n) {
-      NNB_PROF_T0;
-      const int hq = kvh * p.group + n / n_qt, qt = first_qt + n % n_qt;
-      const int qi = qt * BQ + row;
-      const bool row_ok = qi < p.T;
-      const size_t stat = ((size_t)b * p.H + hq) * p.T + (row_ok ? qi : 0);
-      const float L = row_ok ? p.lse[stat] * kLog2e : 0.f;
-      const float D = row_ok ? p.delta[stat] : 0.f;
-      if (!mbar_wait(bar_sdp, n & 1, abort_flag)) ok = false;  // made uniform at the barrier below
-      tc_fence_after();
-      NNB_PROF_ADD(0);
-      // Only tiles on the diagonal, past the end of the sequence, or with padded query rows need the
-      // per-element mask; every other tile takes the branch-free version (5 instructions per element).
-      const bool need_mask = key0 + 63 > qt * BQ || key0 + 63 >= p.T || qt * BQ + BQ > p.T;
-      const float Ds = D * p.scale;
-      auto tile = [&](auto masked) {
-        constexpr bool kMask = decltype(masked)::value;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t rs[32], rp[32];
-          tmem_ld_32x32b_x32(t_lane + kColS + half * 64 + c * 32, rs);
-          tmem_ld_32x32b_x32(t_lane + kColdP + half * 64 + c * 32, rp);
-          tmem_ld_wait();
-          uint32_t pk[16], dk[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float pv[2], dv[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              float prob = exp2f(__uint_as_float(rs[i + e]) * p.scale_log2 - L);
-              if (kMask) {
-                const int key = key0 + c * 32 + i + e;
-                prob = (row_ok && key <= qi && key < p.T) ? prob : 0.f;
-              }
-              pv[e] = prob;
-              dv[e] = prob * (__uint_as_float(rp[i + e]) * p.scale - Ds);
-            }
-            __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]), d2 = __floats2bfloat162_rn(dv[0], dv[1]);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
-            dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
-          }
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const int chunk = ((c * 4 + jj) ^ sw) << 4;
-            *reinterpret_cast<uint4*>(my_p + chunk) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
-            *reinterpret_cast<uint4*>(my_ds + chunk) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
-          }
-        }
-      };
-      if (ok) {
-        if (need_mask) tile(std::true_type{});
-        else tile(std::false_type{});
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_pds);
-      NNB_PROF_ADD(1);
-      // dQ partial tile: TMEM -> swizzled fp32 staging (one [128 x 32] box per half) -> TMA reduce-add
-      if (ok && !mbar_wait(bar_dq, n & 1, abort_flag)) ok = false;
+    // dQ partial tile of visit m: TMEM (score buffer m & 1) -> swizzled fp32 staging (one [128 x 32] box per half) -> TMA
+    // reduce-add. Every compute thread runs it, good or bad, so the two block barriers inside always see all 256 threads.
+    auto drain_dq = [&](int m) {
+      const int hq = kvh * p.group + m / n_qt, qt = first_qt + m % n_qt;
+      if (ok && !mbar_wait(bar_dq, m & 1, abort_flag)) ok = false;
       tc_fence_after();
       if (leader) tma_wait_group_read<0>();      // the previous reduce has finished reading the staging tile
-      NNB_PROF_ADD(2);
-      if (named_barrier_or(1, kComputeThreads, !ok)) { ok = false; fail_role = 3; break; }  // all leave together
-      {
+      if (named_barrier_or(1, kComputeThreads, !ok)) ok = false;
+      if (ok) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + kColdQ + half * 32, r);
+        tmem_ld_32x32b_x32(t_lane + kColdQ + (m & 1) * BKV + half * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
@@ -254,13 +234,97 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_arrive(bar_dqr);
       fence_proxy_async_smem();
       named_barrier_sync(1, kComputeThreads);
-      if (leader) {
+      if (leader && ok) {
         tma_reduce_add_4d(&tmdQacc, s_base + kOffStage, 0, hq, qt * BQ, b);
         tma_reduce_add_4d(&tmdQacc, s_base + kOffStage + kTile16, 32, hq, qt * BQ, b);
         tma_commit_group();
       }
+    };
+    for (int n = 0; n < iters; ++n) {
+      NNB_PROF_T0;
+      const int hq = kvh * p.group + n / n_qt, qt = first_qt + n % n_qt;
+      const int qi = qt * BQ + row;
+      const bool row_ok = qi < p.T;
+      const size_t stat = ((size_t)b * p.H + hq) * p.T + (row_ok ? qi : 0);
+      const float L = row_ok ? p.lse[stat] * kLog2e : 0.f;
+      const float D = row_ok ? p.delta[stat] : 0.f;
+      // Only tiles on the diagonal, past the end of the sequence, or with padded query rows need the
+      // per-element mask; every other tile takes the branch-free version.
+      const bool need_mask = key0 + 63 > qt * BQ || key0 + 63 >= p.T || qt * BQ + BQ > p.T;
+      const float Ds = D * p.scale;
+      const uint32_t t_s = t_lane + kColS + (n & 1) * BKV + half * 64;
+      float prob[64];  // P of this thread's 64 keys, kept in fp32 from phase A to phase B
+      // ---- phase A: P = exp2(S scale log2e - L log2e)
+      if (ok && !mbar_wait(bar_s + 8 * (n & 1), (n >> 1) & 1, abort_flag)) ok = false;
+      tc_fence_after();
+      NNB_PROF_ADD(0);
+      auto phase_a = [&](auto masked) {
+        constexpr bool kMask = decltype(masked)::value;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], pk[16];
+          tmem_ld_32x32b_x32(t_s + c * 32, rs);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float pr = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - L);
+            if (kMask) {
+              const int key = key0 + c * 32 + i;
+              pr = (row_ok && key <= qi && key < p.T) ? pr : 0.f;
+            }
+            prob[c * 32 + i] = pr;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(prob[c * 32 + i], prob[c * 32 + i + 1]);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4*>(my_p + (((c * 4 + jj) ^ sw) << 4)) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+        }
+      };
+      if (ok) {
+        if (need_mask) phase_a(std::true_type{});
+        else phase_a(std::false_type{});
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar_p);
+      NNB_PROF_ADD(1);
+      // ---- the previous visit's dQ leaves while the tensor core works on dV(n) and S(n + 1)
+      if (n > 0) drain_dq(n - 1);
+      NNB_PROF_ADD(2);
+      // ---- phase B: dS = P (dP scale - D scale)
+      if (ok && !mbar_wait(bar_dp, n & 1, abort_flag)) ok = false;
+      tc_fence_after();
       NNB_PROF_ADD(3);
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rp[32], dk[16];
+          tmem_ld_32x32b_x32(t_lane + kColdP + half * 64 + c * 32, rp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float d0 = prob[c * 32 + i] * (__uint_as_float(rp[i]) * p.scale - Ds);
+            const float d1 = prob[c * 32 + i + 1] * (__uint_as_float(rp[i + 1]) * p.scale - Ds);
+            __nv_bfloat162 d2 = __floats2bfloat162_rn(d0, d1);
+            dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4*>(my_ds + (((c * 4 + jj) ^ sw) << 4)) = make_uint4(dk[4 * jj], dk[4 * jj + 1], dk[4 * jj + 2], dk[4 * jj + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar_ds);
+      NNB_PROF_ADD(4);
+      if (named_barrier_or(2, kComputeThreads, !ok)) { ok = false; fail_role = 3; break; }  // all leave together
     }
+    if (iters > 0) drain_dq(iters - 1);
+    if (!ok && fail_role == 0) fail_role = 3;
     NNB_PROF_FLUSH_N(iters);
     // dV (half 0) and dK (half 1) of this key tile: TMEM -> bf16 staging (reuse the P / dS tiles) -> TMA store
     if (ok && iters > 0) {
@@ -467,7 +531,7 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
     }
     configured = true;
   }
-  dim3 grid((T + BKV - 1) / BKV, KVH, B);
+  dim3 grid(KVH, B, (T + BKV - 1) / BKV);
   flash_bwd_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   NNB_LAUNCH_OK("flash_bwd");
   flash_dq_convert_kernel<<<(unsigned)((rows * (HD / 16) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows,

@@ -79,7 +79,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   float* s_ld = reinterpret_cast<float*>(smem + C::kOffLD);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int kt = blockIdx.z, kvh = blockIdx.x, b = blockIdx.y;  // key tile slowest: the heavy CTAs (early keys) are scheduled first
   const int first_qb = (kt * BKV) / BQ;
   const int n_qb = p.n_q_blocks - first_qb;
   const int iters = n_qb * p.group;
@@ -449,7 +449,7 @@ int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, con
     }
     configured = true;
   }
-  dim3 grid((T + BKV - 1) / BKV, KVH, B);
+  dim3 grid(KVH, B, (T + BKV - 1) / BKV);
   flash_bwd_t_kernel<HD><<<grid, kThreads, C::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   NNB_LAUNCH_OK("flash_bwd_t");
   flash_dq_convert_t_kernel<HD><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq,

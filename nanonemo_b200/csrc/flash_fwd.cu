@@ -83,8 +83,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = p.n_q_tiles - 1 - blockIdx.x;  // heaviest (latest) query tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Longest-job-first over the WHOLE grid: the query tile is the slowest-varying block index, so every CTA of the latest
+  // (heaviest) query tile is scheduled before any of the next one and the kernel ends on the one-key-tile CTAs.
+  const int qt = p.n_q_tiles - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.H / p.KVH);
   const int kv_total = (p.T + BN - 1) / BN;
   const int n_kv = min(((qt + 1) * BQ + BN - 1) / BN, kv_total);  // KV tiles holding keys <= the tile's last row
@@ -209,7 +211,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     }
     configured = true;
   }
-  dim3 grid(p.n_q_tiles, p.H, p.B);
+  dim3 grid(p.H, p.B, p.n_q_tiles);
   kern<<<grid, kThreads, FCfg<HD>::kSmem, st>>>(tq, tk, tv, to, p);
   return 0;
 }
