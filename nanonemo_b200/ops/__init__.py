@@ -3,6 +3,12 @@
 (``impl="sm100"``) from ``nanonemo_b200/csrc``. There is no third backend and no runtime probing:
 asking for ``sm100`` without the built library, or off a CUDA device, raises.
 
+The sm100 kernels are bound once, as ``torch.library`` custom operators with fake implementations and autograd
+formulas (``ops/library.py``), and that is what these functions call. The one exception is a parameter that lives in
+the trainer's flat parameter store (it carries ``_main_grad``): its operators run as ``autograd.Function``s that
+accumulate the weight gradient in place in the flat fp32 buffer and tell the strategy when it is complete — what a
+functional operator may not do. Both routes launch the same kernels.
+
 Operator contracts follow the reference kernels (nanonemo/kernels/triton/*.py,
 nanonemo/kernels/cuda/*.py): ``add_rms_norm(x, delta, w, eps) -> (y, h)``, RoPE on Q and K in one
 launch, ``swiglu``, ``flash_attn(q, k, v)`` reading KV heads directly, ``linear_cross_entropy``.
@@ -62,6 +68,11 @@ def _need_cuda(t: torch.Tensor, op: str):
         raise RuntimeError(f"{op}: impl='sm100' needs a CUDA tensor (got {t.device}); use impl='torch' on CPU")
 
 
+def in_flat_store(weight) -> bool:
+    """True for a parameter of the trainer's flat store: its gradient is accumulated in place by the backward kernels."""
+    return getattr(weight, "_main_grad", None) is not None
+
+
 def linear(x, weight, impl="torch"):
     if impl == "torch":
         return F.linear(x, weight)
@@ -70,18 +81,32 @@ def linear(x, weight, impl="torch"):
         from nanonemo_b200.fp8 import linear_mxfp8
 
         return linear_mxfp8(x, weight)
-    from nanonemo_b200.ops.gemm import linear_sm100
+    if in_flat_store(weight) or getattr(weight, "_shadow", None) is not None:
+        from nanonemo_b200.ops.gemm import linear_sm100
 
-    return linear_sm100(x, weight)
+        return linear_sm100(x, weight)
+    from nanonemo_b200.ops import library
+
+    return library.linear(x, weight)
 
 
 def add_rms_norm(x, delta, weight, eps, impl="torch"):
     if impl == "torch":
         return add_rms_norm_torch(x, delta, weight, eps)
     _need_cuda(x, "add_rms_norm")
-    from nanonemo_b200.ops.rmsnorm import add_rms_norm as f
+    from nanonemo_b200.ops import rmsnorm
 
-    return f(x, delta, weight, eps)
+    if in_flat_store(weight):
+        return rmsnorm.add_rms_norm(x, delta, weight, eps)
+    from nanonemo_b200.ops import library
+
+    y_dtype = rmsnorm._y_dtype(x, delta)
+    if delta is not None and delta.dtype != y_dtype:
+        delta = delta.to(y_dtype)
+    if x.dtype not in (torch.float32, y_dtype):
+        x = x.float()
+    y, h, _ = library.add_rms_norm(x, delta, weight, eps, library._DT_CODE[y_dtype])
+    return y, h
 
 
 def rope_qkv(qkv, cos, sin, n_heads, n_kv_heads, head_dim, impl="torch"):
@@ -94,9 +119,11 @@ def rope_qkv(qkv, cos, sin, n_heads, n_kv_heads, head_dim, impl="torch"):
         k = rope_torch(k.reshape(B, T, n_kv_heads, head_dim), cos, sin, seq_dim=1).reshape(B, T, kd)
         return torch.cat((q, k, v), dim=-1)
     _need_cuda(qkv, "rope_qkv")
-    from nanonemo_b200.ops.rope import rope_qkv as f
+    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops.rope import _tables
 
-    return f(qkv, cos, sin, n_heads, n_kv_heads, head_dim)
+    c, s = _tables(cos, sin, qkv.shape[1])
+    return library.rope_qkv(qkv, c, s, n_heads, n_kv_heads, head_dim)
 
 
 def apply_rope_qk(q, k, cos, sin, impl="torch"):
@@ -104,9 +131,15 @@ def apply_rope_qk(q, k, cos, sin, impl="torch"):
     if impl == "torch":
         return rope_torch(q, cos, sin, seq_dim=1), rope_torch(k, cos, sin, seq_dim=1)
     _need_cuda(q, "apply_rope_qk")
-    from nanonemo_b200.ops.rope import apply_rope_qk as f
+    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops.rope import _tables
 
-    return f(q, k, cos, sin)
+    B, T, H, hd = q.shape
+    KVH = k.shape[2]
+    c, s = _tables(cos, sin, T)
+    packed = torch.cat((q.reshape(B * T, H * hd), k.reshape(B * T, KVH * hd)), dim=-1)
+    out = library.rope_rows(packed, c, s, T, H + KVH, hd, 1.0)
+    return out[:, :H * hd].reshape(B, T, H, hd), out[:, H * hd:].reshape(B, T, KVH, hd)
 
 
 def attention_packed(qkv, n_heads, n_kv_heads, head_dim, impl="torch", backend=SDPBackend.MATH):
@@ -120,9 +153,11 @@ def attention_packed(qkv, n_heads, n_kv_heads, head_dim, impl="torch", backend=S
         v = v.view(B, T, n_kv_heads, head_dim).transpose(1, 2)
         return attention_torch(q, k, v, backend).transpose(1, 2).reshape(B, T, qd)
     _need_cuda(qkv, "attention_packed")
-    from nanonemo_b200.ops.attention import flash_attn_packed
+    from nanonemo_b200.ops import library
 
-    return flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)
+    if qkv.dtype != torch.bfloat16:  # the attention kernels are bf16: fp16 / fp32 inputs are converted and the result converted back
+        return library.flash_attn_packed(qkv.to(torch.bfloat16), n_heads, n_kv_heads, head_dim)[0].to(qkv.dtype)
+    return library.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)[0]
 
 
 def flash_attn(q, k, v, impl="sm100"):
@@ -130,18 +165,19 @@ def flash_attn(q, k, v, impl="sm100"):
     if impl == "torch":
         return attention_torch(q, k, v)
     _need_cuda(q, "flash_attn")
-    from nanonemo_b200.ops.attention import flash_attn as f
+    from nanonemo_b200.ops import library
 
-    return f(q, k, v)
+    bf = torch.bfloat16  # the attention kernels are bf16: other dtypes are converted and the result converted back
+    return library.flash_attn(q.to(bf), k.to(bf), v.to(bf))[0].to(q.dtype)
 
 
 def swiglu(g, u, impl="torch"):
     if impl == "torch":
         return swiglu_torch(g, u)
     _need_cuda(g, "swiglu")
-    from nanonemo_b200.ops.swiglu_act import swiglu as f
+    from nanonemo_b200.ops import library
 
-    return f(g, u)
+    return library.swiglu_gu(g, u if u.dtype == g.dtype else u.to(g.dtype))
 
 
 def swiglu_packed(gu, impl="torch"):
@@ -150,9 +186,9 @@ def swiglu_packed(gu, impl="torch"):
         g, u = gu.chunk(2, dim=-1)
         return swiglu_torch(g, u)
     _need_cuda(gu, "swiglu_packed")
-    from nanonemo_b200.ops.swiglu_act import swiglu_packed as f
+    from nanonemo_b200.ops import library
 
-    return f(gu)
+    return library.swiglu(gu)
 
 
 def fused_ok() -> bool:
@@ -163,34 +199,56 @@ def fused_ok() -> bool:
 
 
 def qkv_rope_attention(x, weight, cos, sin, n_heads, n_kv_heads, head_dim):
-    """Packed QKV projection + RoPE (GEMM epilogue) + causal GQA attention as one autograd node (sm100 only)."""
+    """Packed QKV projection + RoPE (GEMM epilogue) + causal GQA attention (sm100 only)."""
     _need_cuda(x, "qkv_rope_attention")
-    from nanonemo_b200.ops.fused_block import qkv_rope_attention as f
+    if in_flat_store(weight) or getattr(weight, "_shadow", None) is not None:
+        from nanonemo_b200.ops.fused_block import qkv_rope_attention as f
 
-    return f(x, weight, cos, sin, n_heads, n_kv_heads, head_dim)
+        return f(x, weight, cos, sin, n_heads, n_kv_heads, head_dim)  # one autograd node, inverse RoPE inside the attention backward
+    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops.rope import _tables
+
+    B, T, _ = x.shape
+    c, s = _tables(cos, sin, T)
+    x2 = x.reshape(B * T, -1).to(torch.bfloat16).contiguous()
+    qkv = library.gemm_rope(x2, weight, c, s, T, (n_heads + n_kv_heads) * head_dim, head_dim).view(B, T, -1)
+    return library.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)[0]
 
 
 def linear_swiglu(x, weight):
     """gate||up projection with silu(gate) * up written by the GEMM epilogue (sm100 only)."""
     _need_cuda(x, "linear_swiglu")
-    from nanonemo_b200.ops.fused_block import linear_swiglu as f
+    if in_flat_store(weight) or getattr(weight, "_shadow", None) is not None:
+        from nanonemo_b200.ops.fused_block import linear_swiglu as f
 
-    return f(x, weight)
+        return f(x, weight)
+    from nanonemo_b200.ops import library
+
+    x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    return library.gemm_swiglu(x2, weight)[1].view(*x.shape[:-1], weight.shape[0] // 2)
 
 
 def embedding(idx, weight, impl="torch"):
     if impl == "torch":
         return F.embedding(idx, weight)
     _need_cuda(weight, "embedding")
-    from nanonemo_b200.ops.embed import embedding as f
+    if in_flat_store(weight):
+        from nanonemo_b200.ops.embed import embedding as f
 
-    return f(idx, weight)
+        return f(idx, weight)
+    from nanonemo_b200.ops import library
+
+    return library.embedding(idx, weight, True)
 
 
 def linear_cross_entropy(x, weight, targets, impl="sm100", chunk_rows=None):
     """Mean next-token cross entropy of ``x @ weight.T`` without materialising the full logits."""
     if impl == "torch" or not x.is_cuda:
         return linear_cross_entropy_torch(x, weight, targets)
-    from nanonemo_b200.ops.linear_ce import linear_cross_entropy as f
+    if in_flat_store(weight) or getattr(weight, "_shadow", None) is not None:
+        from nanonemo_b200.ops.linear_ce import linear_cross_entropy as f
 
-    return f(x, weight, targets, chunk_rows)
+        return f(x, weight, targets, chunk_rows)
+    from nanonemo_b200.ops import library
+
+    return library.linear_cross_entropy(x, weight, targets, chunk_rows)
