@@ -2,9 +2,12 @@
 //
 // nnb_adamw_flat does, in ONE pass over memory: clip coefficient from the device-resident squared
 // norm, decoupled weight decay (per 256-element block flag), both moment updates, the fp32 master
-// update (same arithmetic as torch.optim.AdamW), the 16-bit compute copy, and zeroing of the
-// gradient for the next step. The reference does this with clip_grad_norm_ + foreach AdamW +
+// update (the operations of torch.optim.AdamW in the same order; this file is compiled WITHOUT
+// --use_fast_math, so the square root and the division are IEEE-rounded and denormal moments are
+// kept), the 16-bit compute copy, and zeroing of the gradient for the next step. The reference does this with clip_grad_norm_ + foreach AdamW +
 // zero_grad (nanonemo/train/trainer.py:183-193): about a dozen passes and ~10^3 small launches.
+#include <cmath>
+
 #include "common.cuh"
 
 // ---------------------------------------------------------------- sum of squares
@@ -109,8 +112,9 @@ extern "C" int nnb_adamw_flat(void* p, void* g, void* m, void* v, void* shadow, 
   NNB_REQUIRE(n % 256 == 0, "adamw_flat: n=%lld must be a multiple of 256", n);
   NNB_REQUIRE(step >= 1, "adamw_flat: step must be >= 1");
   if (n == 0) return 0;
-  const float bc1 = 1.f - powf(beta1, (float)step);
-  const float bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
+  // bias corrections in double on the host, as torch.optim.AdamW computes them (python floats)
+  const float bc1 = (float)(1.0 - pow((double)beta1, (double)step));
+  const float bc2_sqrt = (float)sqrt(1.0 - pow((double)beta2, (double)step));
   const long long n4 = n / 4;
   const int blocks = (int)min((n4 + 255) / 256, (long long)nnb_num_sms() * 8);
   if (shadow == nullptr || shadow_dtype == NNB_BF16) {

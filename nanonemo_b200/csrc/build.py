@@ -21,6 +21,9 @@ LIB = HERE / "libnanonemo_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC", "-DNNB_ARCH=100",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+# Translation units whose arithmetic has to match a PyTorch reference operation for operation (the optimizer update):
+# IEEE division and square root, no flush-to-zero. They are bandwidth-bound, so this costs nothing measurable.
+PRECISE = {"adamw.cu", "comm.cu"}  # comm.cu: the reduce-scatter that applies AdamW in its epilogue
 
 
 def nvcc() -> str:
@@ -49,7 +52,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     def compile_one(job):
         src, obj = job
         extra = os.environ.get("NANONEMO_NVCC_EXTRA", "").split()  # e.g. -DNNB_PROFILE: in-kernel phase timers of the attention kernels
-        cmd = [nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
+        flags = [f for f in NVCC_FLAGS if not (src.name in PRECISE and f == "--use_fast_math")]
+        cmd = [nvcc(), *ARCH_FLAGS, *flags, *extra, "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         (objdir / (src.stem + ".ptxas.log")).write_text(r.stderr)
         return src, r

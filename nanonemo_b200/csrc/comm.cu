@@ -23,6 +23,8 @@
 // Nothing here waits on a kernel of the same GPU: one rank = one process = one GPU.
 //
 // The reference reaches NCCL through torch DDP / FSDP2 / DTensor (nanonemo/distributed/*.py).
+#include <cmath>
+
 #include "comm.cuh"
 
 namespace {
@@ -134,11 +136,26 @@ __global__ void __launch_bounds__(256) sumsq_combine_kernel(const float* __restr
   }
 }
 
-// out[i] = scale * sum_r data[r][lo + rank*per + i]; sumsq_out += sum(out^2) (one atomic per block).
+// Sharded optimizer state of one unit for the reduce-scatter that applies AdamW in its epilogue (no clipping: the update of
+// an element needs nothing but its own reduced gradient). All pointers address this rank's shard of the unit.
+struct ShardAdamW {
+  float* p;                      // fp32 master weights, null = plain reduce-scatter
+  float* m;
+  float* v;
+  void* wire;                    // 16-bit copy that the next all-gather sends, or null
+  const unsigned char* decay;    // one flag per 256 elements
+  float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt;
+  int wire_bf16;
+};
+
+// out[i] = scale * sum_r data[r][lo + rank*per + i] (gradient reduce-scatter of one FSDP unit), plus the squared norm of the
+// reduced shard: added to sumsq_out (one atomic per block) and / or stored per block into every peer's norm table (row
+// `bucket`), as the all-reduce does, so the global norm needs no further collective. With A.p set, the AdamW update of the
+// shard happens right here on the reduced values, which then never travel through memory as a gradient.
 template <int WMAX, int U>
-__global__ void __launch_bounds__(kCommThreads, 3) reduce_scatter_f32_kernel(Peers P, float* out, float* sumsq_out, int rank, int world,
-                                                                             long long lo, long long per, float scale,
-                                                                             uint32_t* epochs, int slot_blocks,
+__global__ void __launch_bounds__(kCommThreads, 3) reduce_scatter_f32_kernel(Peers P, Peers NP, float* out, float* sumsq_out, int rank,
+                                                                             int world, long long lo, long long per, float scale,
+                                                                             uint32_t* epochs, int slot_blocks, int bucket, ShardAdamW A,
                                                                              unsigned long long timeout_ns, int* status) {
   __shared__ float s_part[kCommThreads / 32];
   const uint32_t epoch = next_block_epoch(epochs);
@@ -164,19 +181,49 @@ __global__ void __launch_bounds__(kCommThreads, 3) reduce_scatter_f32_kernel(Pee
         for (int r = 1; r < WMAX; ++r)
           if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
         acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-        reinterpret_cast<float4*>(out)[i] = acc;
         ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        if (A.p == nullptr) {
+          reinterpret_cast<float4*>(out)[i] = acc;
+        } else {
+          float4 pp = reinterpret_cast<float4*>(A.p)[i], mm = reinterpret_cast<float4*>(A.m)[i], vv = reinterpret_cast<float4*>(A.v)[i];
+          const float decay = A.decay[i >> 6] ? 1.f - A.lr * A.wd : 1.f;
+          const float step_size = A.lr / A.bc1;
+          float* Pp = &pp.x; const float* G = &acc.x; float* Mo = &mm.x; float* V = &vv.x;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            Pp[k] *= decay;
+            Mo[k] = Mo[k] + (G[k] - Mo[k]) * (1.f - A.beta1);
+            V[k] = V[k] * A.beta2 + G[k] * G[k] * (1.f - A.beta2);
+            Pp[k] -= step_size * (Mo[k] / (sqrtf(V[k]) / A.bc2_sqrt + A.eps));
+          }
+          reinterpret_cast<float4*>(A.p)[i] = pp;
+          reinterpret_cast<float4*>(A.m)[i] = mm;
+          reinterpret_cast<float4*>(A.v)[i] = vv;
+          if (A.wire != nullptr) {
+            if (A.wire_bf16) {
+              __nv_bfloat162* w = reinterpret_cast<__nv_bfloat162*>(A.wire) + 2 * i;
+              w[0] = __floats2bfloat162_rn(pp.x, pp.y);
+              w[1] = __floats2bfloat162_rn(pp.z, pp.w);
+            } else {
+              __half2* w = reinterpret_cast<__half2*>(A.wire) + 2 * i;
+              w[0] = __floats2half2_rn(pp.x, pp.y);
+              w[1] = __floats2half2_rn(pp.z, pp.w);
+            }
+          }
+        }
       }
     }
   }
-  if (sumsq_out != nullptr) {
+  if (sumsq_out != nullptr || NP.data[0] != nullptr) {
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x < 32) {
       float v = threadIdx.x < kCommThreads / 32 ? s_part[threadIdx.x] : 0.f;
       v = warp_sum(v);
-      if (threadIdx.x == 0) atomicAdd(sumsq_out, v);
+      if (threadIdx.x == 0 && sumsq_out != nullptr) atomicAdd(sumsq_out, v);
+      if (NP.data[0] != nullptr && (int)threadIdx.x < world)
+        static_cast<float*>(NP.data[threadIdx.x])[((long long)bucket * world + rank) * slot_blocks + blockIdx.x] = v;
     }
   }
   // peers may overwrite their inputs only after everybody has read them
@@ -271,11 +318,12 @@ extern "C" int nnb_sumsq_combine(const void* parts, long long n, void* out, cuda
   return 0;
 }
 
-extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_ptrs, void* out, void* sumsq_out, void* status,
-                                      void* epochs, int rank, int world, long long lo, long long per, float scale, int blocks,
-                                      double timeout_s, cudaStream_t st) {
-  Peers P;
+static int launch_reduce_scatter(void* const* data_ptrs, void* const* flag_ptrs, void* const* norm_ptrs, void* out, void* sumsq_out,
+                                 void* status, void* epochs, int rank, int world, long long lo, long long per, float scale, int bucket,
+                                 int blocks, double timeout_s, const ShardAdamW& A, cudaStream_t st) {
+  Peers P, NP;
   if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  if (fill_peers(NP, norm_ptrs, flag_ptrs, world) != 0) return -1;
   NNB_REQUIRE(lo % 4 == 0 && per % 4 == 0, "reduce_scatter: range must be 16-byte aligned");
   NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "reduce_scatter: bad block count %d or no epoch counters", blocks);
   if (per == 0) return 0;
@@ -285,11 +333,38 @@ extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_
   int* stw = static_cast<int*>(status);
   uint32_t* ep = static_cast<uint32_t*>(epochs);
   const unsigned long long tns = timeout_ns_of(timeout_s);
-  if (world <= 2) reduce_scatter_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
-  else if (world <= 4) reduce_scatter_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
-  else reduce_scatter_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, o, sq, rank, world, lo, per, scale, ep, blocks, tns, stw);
+  if (world <= 2) reduce_scatter_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
+  else if (world <= 4) reduce_scatter_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
+  else reduce_scatter_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
   NNB_LAUNCH_OK("reduce_scatter_f32");
   return 0;
+}
+
+// norm_ptrs: null, or every rank's norm table (see nnb_allreduce_f32); `bucket` picks the row this call fills.
+extern "C" int nnb_reduce_scatter_f32(void* const* data_ptrs, void* const* flag_ptrs, void* const* norm_ptrs, void* out, void* sumsq_out,
+                                      void* status, void* epochs, int rank, int world, long long lo, long long per, float scale,
+                                      int bucket, int blocks, double timeout_s, cudaStream_t st) {
+  ShardAdamW none{};
+  NNB_REQUIRE(out != nullptr, "reduce_scatter: no output buffer");
+  return launch_reduce_scatter(data_ptrs, flag_ptrs, norm_ptrs, out, sumsq_out, status, epochs, rank, world, lo, per, scale, bucket,
+                               blocks, timeout_s, none, st);
+}
+
+// Reduce-scatter whose epilogue IS the sharded AdamW step (for training without gradient clipping): p / m / v: this rank's
+// fp32 shard of the unit (per elements), wire: its 16-bit copy for the next parameter all-gather (or null), decay_flags: one
+// byte per 256 elements. The reduced gradient is never written; its squared norm still goes to the norm table for logging.
+extern "C" int nnb_reduce_scatter_adamw(void* const* data_ptrs, void* const* flag_ptrs, void* const* norm_ptrs, void* p, void* m, void* v,
+                                        void* wire, const void* decay_flags, void* status, void* epochs, int rank, int world,
+                                        long long lo, long long per, float scale, int bucket, int blocks, double timeout_s, float lr,
+                                        float beta1, float beta2, float eps, float wd, int step, int wire_dtype, cudaStream_t st) {
+  NNB_REQUIRE(p != nullptr && m != nullptr && v != nullptr && decay_flags != nullptr, "reduce_scatter_adamw: missing optimizer state");
+  NNB_REQUIRE(per % 256 == 0 && step >= 1, "reduce_scatter_adamw: shard of %lld elements must be a multiple of 256, step >= 1", per);
+  NNB_REQUIRE(wire == nullptr || wire_dtype == NNB_BF16 || wire_dtype == NNB_F16, "reduce_scatter_adamw: wire dtype code %d", wire_dtype);
+  ShardAdamW A{static_cast<float*>(p), static_cast<float*>(m), static_cast<float*>(v), wire, static_cast<const unsigned char*>(decay_flags),
+               lr, beta1, beta2, eps, wd, (float)(1.0 - pow((double)beta1, (double)step)),
+               (float)sqrt(1.0 - pow((double)beta2, (double)step)), wire_dtype == NNB_BF16 ? 1 : 0};
+  return launch_reduce_scatter(data_ptrs, flag_ptrs, norm_ptrs, nullptr, nullptr, status, epochs, rank, world, lo, per, scale, bucket,
+                               blocks, timeout_s, A, st);
 }
 
 extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptrs, void* local_full, void* status, void* epochs,

@@ -92,6 +92,30 @@ def gemm_mxfp8(aq, asf, bq, bsf, out=None, out_dtype=torch.bfloat16, accumulate=
     return out
 
 
+# Quantised copies of a weight are made once per optimizer step, not once per forward: every micro-batch of the step, and
+# the dgrad of every one of them, multiplies by the same bytes. The optimizers of this framework call `weights_changed()`
+# after they have rewritten the 16-bit shadow weights; only store-managed weights (they carry `_shadow`) are cached.
+_WEIGHT_EPOCH = 0
+
+
+def weights_changed() -> None:
+    global _WEIGHT_EPOCH
+    _WEIGHT_EPOCH += 1
+
+
+def quantized_weight(weight: torch.Tensor, w16: torch.Tensor):
+    """(wq, ws, wtq, wts) of `w16` [N, K]: blocks along K for fprop, the transposed copy with blocks along N for dgrad."""
+    managed = getattr(weight, "_shadow", None) is w16
+    if managed:
+        hit = getattr(weight, "_mx_cache", None)
+        if hit is not None and hit[0] == _WEIGHT_EPOCH and hit[1] == w16.data_ptr():
+            return hit[2]
+    q = quantize_mx(w16, True, True)
+    if managed:
+        weight._mx_cache = (_WEIGHT_EPOCH, w16.data_ptr(), q)
+    return q
+
+
 def _tensor_core_ok(*dims) -> bool:
     return os.environ.get("NANONEMO_FP8_EMULATE", "0") != "1" and all(d % 128 == 0 for d in dims)
 
@@ -107,7 +131,9 @@ class _LinearMXFP8(torch.autograd.Function):
         need_w, need_x = ctx.needs_input_grad[1], ctx.needs_input_grad[0]
         if ctx.real:
             xq, xs, xtq, xts = quantize_mx(x2, True, need_w)           # x along K_in (fprop); x^T along tokens (wgrad)
-            wq, ws, wtq, wts = quantize_mx(w16, True, need_x)          # W along K_in (fprop); W^T along N_out (dgrad)
+            wq, ws, wtq, wts = quantized_weight(weight, w16)           # W along K_in (fprop); W^T along N_out (dgrad)
+            if not need_x:
+                wtq = wts = None
             y = gemm_mxfp8(xq, xs, wq, ws)
             ctx.save_for_backward(weight, *(t for t in (xtq, xts, wtq, wts) if t is not None))
             ctx.flags = (need_w, need_x)

@@ -18,6 +18,13 @@ from torch import nn
 ALIGN = 256  # elements; keeps every view 1 KiB aligned in fp32 (16-byte TMA rule holds for bf16 too)
 
 
+def _shadow_rewritten() -> None:
+    """The 16-bit compute copies of the weights have new values: cached quantised copies of them are stale."""
+    from nanonemo_b200 import fp8
+
+    fp8.weights_changed()
+
+
 def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
@@ -88,6 +95,7 @@ class FlatParams:
         """Re-derive the low-precision compute copy from the fp32 master weights."""
         if self.shadow is not None:
             self.shadow.copy_(self.master)
+            _shadow_rewritten()
 
     def grad_sumsq(self) -> torch.Tensor:
         """Sum of squared gradient entries as a device scalar (fp32), one pass over the flat buffer."""
@@ -138,3 +146,4 @@ class FlatParams:
                    None if self.shadow is None else self.shadow[lo:hi], self.decay_flags[lo // ALIGN:hi // ALIGN],
                    lr=g0["lr"], beta1=g0["betas"][0], beta2=g0["betas"][1], eps=g0["eps"], weight_decay=self._wd,
                    step=step, grad_norm_sq=grad_norm_sq, max_norm=max_norm, zero_grad=True)
+        _shadow_rewritten()

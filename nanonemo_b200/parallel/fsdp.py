@@ -69,6 +69,7 @@ class FSDPStrategy(LocalStrategy):
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self.sumsq = torch.zeros((), dtype=torch.float32, device=self.device)
         self._rs_done = []
+        self._update_in_rs = None  # AdamW hyper-parameters of the current step when the update rides in the reduce-scatter
         self.gather_all(initial=True)
 
     # ------------------------------------------------------------------ layout
@@ -106,6 +107,7 @@ class FSDPStrategy(LocalStrategy):
             self.symm_wire = SymmetricBuffer(self.shard_numel, self.param_dtype, dev, self.group)
             self.wire = self.symm_wire.tensor
             self.comm = SymmetricComm(dev, self.group, self.rank, self.world)
+            self.comm.enable_norm_parts()  # the reduce-scatter kernels leave the squared norm of every reduced shard here
         else:
             self.grad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
             self.wire = torch.zeros(self.shard_numel, dtype=self.param_dtype, device=dev)
@@ -205,7 +207,15 @@ class FSDPStrategy(LocalStrategy):
             ev.record()
             self.comm_stream.wait_event(ev)
             with torch.cuda.stream(self.comm_stream):
-                self.comm.reduce_scatter(self.symm_grad, out, self.sumsq, u.lo, per, 1.0 / self.world)
+                bucket = self.units.index(u)
+                if self._update_in_rs is not None:
+                    # no clipping: the AdamW step of this unit's shard is the epilogue of its reduce-scatter
+                    h = self._update_in_rs
+                    self.comm.reduce_scatter_adamw(self.symm_grad, self.shard[s0:s1], self.exp_avg[s0:s1], self.exp_avg_sq[s0:s1],
+                                                   self.wire[s0:s1] if self.param_dtype != torch.float32 else None,
+                                                   self.decay_flags[s0 // ALIGN:s1 // ALIGN], u.lo, per, 1.0 / self.world, bucket, **h)
+                else:
+                    self.comm.reduce_scatter(self.symm_grad, out, None, u.lo, per, 1.0 / self.world, bucket=bucket)
             self.launches += 1
         elif self.cuda:
             ev = torch.cuda.Event()
@@ -271,6 +281,19 @@ class FSDPStrategy(LocalStrategy):
             self._gather(self.units[1])
         return nullcontext()
 
+    def begin_step(self, opt, grad_clip) -> None:
+        """Called before the micro-batches of an optimizer step. Without gradient clipping the update of an element needs
+        only its own reduced gradient, so the reduce-scatter kernels of this step apply AdamW in their epilogue (the plain
+        1-D layout only: under the 2-D mesh some shards still need a reduction over the tensor-parallel group first)."""
+        self._update_in_rs = None
+        no_clip = grad_clip is None or grad_clip <= 0
+        if self.fused and no_clip and type(self) is FSDPStrategy:
+            if not hasattr(self, "_opt"):
+                self.set_weight_decay(opt)
+            g0 = opt.param_groups[0]
+            self._update_in_rs = dict(lr=g0["lr"], beta1=g0["betas"][0], beta2=g0["betas"][1], eps=g0["eps"],
+                                      weight_decay=self._wd, step=self.opt_step + 1)
+
     def finish_grads(self):
         for u in self.units:
             if u not in self._rs_done:
@@ -279,7 +302,13 @@ class FSDPStrategy(LocalStrategy):
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
+    def local_sumsq(self):
+        """Fused path: the norm table already holds every rank's share, summed in a fixed order (no collective)."""
+        return self.comm.norm_sq(len(self.units)).clone()
+
     def reduce_sumsq(self, sumsq):
+        if self.fused:
+            return sumsq  # already global (see local_sumsq)
         dist.all_reduce(sumsq, group=self.group)
         return sumsq
 
@@ -306,26 +335,32 @@ class FSDPStrategy(LocalStrategy):
         if not hasattr(self, "_opt"):
             self.set_weight_decay(opt)
         self.finish_grads()
+        clip = grad_clip if grad_clip is not None and grad_clip > 0 else None
         if self.fused:
-            sumsq = self.sumsq.clone()
+            # every reduce-scatter kernel left the squared norm of its reduced shard, for every rank, in the norm table
+            sumsq = self.local_sumsq()
         else:
             sumsq = self.shard_grad.pow(2).sum()
         sumsq = self.reduce_sumsq(sumsq)
         norm = sumsq.sqrt()
         self.opt_step += 1
         g0 = opt.param_groups[0]
-        if self.fused:
+        if self._update_in_rs is not None:
+            self._update_in_rs = None  # the reduce-scatter kernels of this step already applied the update
+            if self.param_dtype == torch.float32:
+                self.wire.copy_(self.shard)
+        elif self.fused:
             from nanonemo_b200.ops.adamw import adamw_flat
 
             adamw_flat(self.shard, self.shard_grad, self.exp_avg, self.exp_avg_sq,
                        self.wire if self.param_dtype != torch.float32 else None, self.decay_flags, lr=g0["lr"],
                        beta1=g0["betas"][0], beta2=g0["betas"][1], eps=g0["eps"], weight_decay=self._wd,
-                       step=self.opt_step, grad_norm_sq=sumsq, max_norm=grad_clip, zero_grad=False)
+                       step=self.opt_step, grad_norm_sq=sumsq, max_norm=clip, zero_grad=False)
             if self.param_dtype == torch.float32:
                 self.wire.copy_(self.shard)
             self.launches += 1
         else:
-            coef = (grad_clip / (norm + 1e-6)).clamp(max=1.0)
+            coef = (clip / (norm + 1e-6)).clamp(max=1.0) if clip is not None else 1.0
             g = self.shard_grad * coef
             b1, b2 = g0["betas"]
             decay = self.decay_flags.repeat_interleave(ALIGN).to(torch.float32) * (g0["lr"] * self._wd)
@@ -338,6 +373,9 @@ class FSDPStrategy(LocalStrategy):
             self.wire.copy_(self.shard)
         self.grad.zero_()
         self.sumsq.zero_()
+        from nanonemo_b200 import fp8
+
+        fp8.weights_changed()  # the gathered 16-bit weights are about to be replaced
         for u in self.units:
             u.gathered = False
         # the root and (with prefetch) the first block are needed at once: start gathering now
@@ -427,6 +465,9 @@ class FSDPTPStrategy(FSDPStrategy):
             for a, b in self.rep_ranges:
                 self.shard_grad[a:b].copy_(flat[o:o + b - a])
                 o += b - a
+
+    def local_sumsq(self):
+        return self.sumsq.clone()  # unused placeholder: reduce_sumsq below recomputes after the tensor-parallel reduction
 
     def reduce_sumsq(self, sumsq):
         if self.fused:  # the reduce-scatter kernel summed the squares before the TP reduction: recompute

@@ -117,6 +117,9 @@ class LocalStrategy:
         return loss
 
     # -- per optimizer step
+    def begin_step(self, opt, grad_clip) -> None:
+        """Called before the first micro-batch of an optimizer step (a layout may plan its collectives around the update)."""
+
     def finish_grads(self):
         """Block the compute stream until every gradient collective of this step has landed."""
 
@@ -132,7 +135,7 @@ class LocalStrategy:
         if store is None:
             if scaler:
                 scaler.unscale_(opt)
-            norm = torch.nn.utils.clip_grad_norm_(self.parameters_for_clip(), grad_clip)
+            norm = torch.nn.utils.clip_grad_norm_(self.parameters_for_clip(), grad_clip if grad_clip and grad_clip > 0 else float("inf"))
             if hasattr(norm, "full_tensor"):
                 norm = norm.full_tensor()
             if scaler:
@@ -146,10 +149,12 @@ class LocalStrategy:
             scaler.unscale_(opt)
         sumsq = self.global_sumsq()
         norm = sumsq.sqrt()
+        clip = grad_clip if grad_clip is not None and grad_clip > 0 else None  # <= 0 / None: the norm is only reported
         if store.fused_ok and scaler is None and hasattr(opt, "store"):
-            opt.step(grad_norm_sq=sumsq, max_norm=grad_clip)  # clips, updates, refreshes the shadow, zeroes grads
+            opt.step(grad_norm_sq=sumsq if clip is not None else None, max_norm=clip)  # clips, updates, refreshes the shadow, zeroes grads
             return norm
-        self.scale_grads_((grad_clip / (norm + 1e-6)).clamp(max=1.0))
+        if clip is not None:
+            self.scale_grads_((clip / (norm + 1e-6)).clamp(max=1.0))
         if scaler:
             scaler.step(opt)
             scaler.update()

@@ -93,10 +93,7 @@ class SymmetricComm:
         leaves the squared norm of every reduced slice in row `bucket` of the partial-norm table of every rank."""
         from nanonemo_b200.ops import _lib
 
-        with_norm = bucket >= 0 and self.norm_parts is not None
-        assert bucket < MAX_NORM_BUCKETS
-        _lib.call("nnb_allreduce_f32", data.ptr_array, self.flags.ptr_array,
-                  self.norm_parts.ptr_array if with_norm else self._null_ptrs,
+        _lib.call("nnb_allreduce_f32", data.ptr_array, self.flags.ptr_array, self._norm_args(bucket),
                   ctypes.c_void_p(data.multicast_ptr if multimem else 0), _lib.ptr(self.status), _lib.ptr(self.epochs),
                   _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo), _lib.i64(hi - lo), _lib.f32(scale),
                   _lib.i32(max(bucket, 0)), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
@@ -111,15 +108,34 @@ class SymmetricComm:
                   _lib.ptr(self._norm_out), ctypes.c_void_p(_lib.stream_ptr()))
         return self._norm_out[0]
 
+    def _norm_args(self, bucket: int):
+        with_norm = bucket >= 0 and self.norm_parts is not None
+        assert bucket < MAX_NORM_BUCKETS
+        return self.norm_parts.ptr_array if with_norm else self._null_ptrs
+
     def reduce_scatter(self, data: "SymmetricBuffer", out: torch.Tensor, sumsq: torch.Tensor | None, lo: int, per: int,
-                       scale: float):
-        """out[i] = scale * sum over ranks of data[lo + rank * per + i]; sumsq += sum(out ** 2)."""
+                       scale: float, bucket: int = -1):
+        """out[i] = scale * sum over ranks of data[lo + rank * per + i]; sumsq += sum(out ** 2) when given; with
+        `bucket` >= 0 the squared norm also goes to row `bucket` of every rank's norm table (see norm_sq)."""
         from nanonemo_b200.ops import _lib
 
-        _lib.call("nnb_reduce_scatter_f32", data.ptr_array, self.flags.ptr_array, _lib.ptr(out), _lib.ptr(sumsq),
-                  _lib.ptr(self.status), _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i64(lo),
-                  _lib.i64(per), _lib.f32(scale), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
-                  ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.call("nnb_reduce_scatter_f32", data.ptr_array, self.flags.ptr_array, self._norm_args(bucket), _lib.ptr(out),
+                  _lib.ptr(sumsq), _lib.ptr(self.status), _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world),
+                  _lib.i64(lo), _lib.i64(per), _lib.f32(scale), _lib.i32(max(bucket, 0)), _lib.i32(self.blocks),
+                  ctypes.c_double(self.timeout_s), ctypes.c_void_p(_lib.stream_ptr()))
+
+    def reduce_scatter_adamw(self, data: "SymmetricBuffer", p, m, v, wire, decay_flags, lo: int, per: int, scale: float, bucket: int,
+                             *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: int):
+        """Gradient reduce-scatter of one unit whose epilogue applies AdamW to this rank's shard (p, m, v: fp32 [per];
+        wire: 16-bit copy or None). For training without clipping; the reduced gradient is never stored."""
+        from nanonemo_b200.ops import _lib
+
+        code = {torch.bfloat16: 1, torch.float16: 2}[wire.dtype] if wire is not None else 1
+        _lib.call("nnb_reduce_scatter_adamw", data.ptr_array, self.flags.ptr_array, self._norm_args(bucket), _lib.ptr(p), _lib.ptr(m),
+                  _lib.ptr(v), _lib.ptr(wire), _lib.ptr(decay_flags), _lib.ptr(self.status), _lib.ptr(self.epochs), _lib.i32(self.rank),
+                  _lib.i32(self.world), _lib.i64(lo), _lib.i64(per), _lib.f32(scale), _lib.i32(max(bucket, 0)), _lib.i32(self.blocks),
+                  ctypes.c_double(self.timeout_s), _lib.f32(lr), _lib.f32(beta1), _lib.f32(beta2), _lib.f32(eps), _lib.f32(weight_decay),
+                  _lib.i32(step), _lib.i32(code), ctypes.c_void_p(_lib.stream_ptr()))
 
     def all_gather(self, shards: "SymmetricBuffer", full: torch.Tensor, src_off_bytes: int, per_bytes: int):
         """full[r * per : (r + 1) * per] = rank r's bytes [src_off, src_off + per) of `shards`."""

@@ -155,6 +155,7 @@ def train_step(strategy: LocalStrategy, opt, loader: TokenLoader, accum: int, gr
     nothing waits for the GPU; the caller checks element 2 when it reads the tensor."""
     model = strategy.step_model
     loss_sum = None
+    strategy.begin_step(opt, grad_clip)
     for i in range(accum):
         x, y = loader.next_batch()
         torch.compiler.cudagraph_mark_step_begin()  # no-op unless a compiled model replays CUDA graphs

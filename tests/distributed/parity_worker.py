@@ -121,6 +121,15 @@ def main():
         ok &= good
         say(f"PARITY world={world} {name}: max |loss - single| = {worst:.4f} {'ok' if good else 'FAIL'}  {[round(x, 4) for x in losses]}")
         dist.barrier()
+    # without gradient clipping the sharded AdamW step runs inside the reduce-scatter kernels
+    single_nc = run_layout(d, "none", {"grad_clip": 0.0}, fake_single=True)
+    for name, par in (("fsdp, update inside the reduce-scatter", "fsdp"), ("ddp, no clipping", "ddp")):
+        losses = run_layout(d, par, {"grad_clip": 0.0})
+        worst = max(abs(a - b) for a, b in zip(losses, single_nc))
+        good = worst <= TOL and all(x == x for x in losses)
+        ok &= good
+        say(f"PARITY world={world} {name}: max |loss - single| = {worst:.4f} {'ok' if good else 'FAIL'}  {[round(x, 4) for x in losses]}")
+        dist.barrier()
     flag = torch.tensor([0.0 if ok else 1.0], device=d.device)
     dist.all_reduce(flag)
     say("PARITY_OK" if flag.item() == 0 else "PARITY_FAILED")
