@@ -259,6 +259,35 @@ __global__ void __launch_bounds__(kCommThreads, 3) allgather_kernel(Peers P, uin
   block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // shards may be rewritten once everybody has copied them
 }
 
+// Small ranges fetched from the ranks that own them, in ONE launch: item i copies `bytes[i]` bytes at `src_off[i]` of rank
+// `src_rank[i]`'s buffer to `dst[i]` (local). Used for the few parameters a unit's first kernel needs before the unit's own
+// all-gather has run (the norm weight in front of a QKV projection that gathers its unit itself). One block per item.
+struct FetchItem {
+  long long src_off, bytes;
+  uint8_t* dst;
+  int src_rank, pad;
+};
+
+__global__ void __launch_bounds__(kCommThreads, 3) peer_fetch_kernel(Peers P, const FetchItem* __restrict__ items, int n_items, int rank,
+                                                                     int world, uint32_t* epochs, int slot_blocks,
+                                                                     unsigned long long timeout_ns, int* status) {
+  const uint32_t epoch = next_block_epoch(epochs);
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // owners' buffers are final
+  if (ok) {
+    for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
+      const FetchItem f = items[it];
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.data[f.src_rank]) + f.src_off);
+      uint4* dst = reinterpret_cast<uint4*>(f.dst);
+      for (long long i = threadIdx.x; i < (f.bytes >> 4); i += blockDim.x) {
+        uint4 v;
+        asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+        dst[i] = v;
+      }
+    }
+  }
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // owners may rewrite once everybody has read
+}
+
 // Exercises the bounded wait: a "world" of two ranks whose flag buffers are both this GPU's buffer, so the
 // slot that the (absent) second rank would write is never written. The wait gives up after `poll_limit`
 // polls, records the status words and the kernel returns normally; the context stays usable.
@@ -379,5 +408,21 @@ extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptr
                                                     static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
                                                     static_cast<int*>(status));
   NNB_LAUNCH_OK("allgather");
+  return 0;
+}
+
+// items: device array of n_items records {int64 src_off, int64 bytes, void* dst, int32 src_rank, int32 pad} (32 bytes each);
+// offsets, sizes and destinations 16-byte aligned. Uses min(n_items, blocks) blocks of the communicator's flag slots.
+extern "C" int nnb_peer_fetch(void* const* data_ptrs, void* const* flag_ptrs, const void* items, int n_items, void* status, void* epochs,
+                              int rank, int world, int blocks, double timeout_s, cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, data_ptrs, flag_ptrs, world) != 0) return -1;
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr && items != nullptr, "peer_fetch: bad arguments");
+  if (n_items <= 0) return 0;
+  static_assert(sizeof(FetchItem) == 32, "FetchItem layout is part of the interface");
+  peer_fetch_kernel<<<min(n_items, blocks), kCommThreads, 0, st>>>(P, static_cast<const FetchItem*>(items), n_items, rank, world,
+                                                                  static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
+                                                                  static_cast<int*>(status));
+  NNB_LAUNCH_OK("peer_fetch");
   return 0;
 }

@@ -73,7 +73,15 @@ struct Params {
   //  mode 2  all-gather -> GEMM: A rows are sharded over the ranks in a symmetric buffer; the first `gather_ctas`
   //          CTAs pull the peers' shards into the local buffer m-block by m-block and publish a ready flag per
   //          m-block; the other CTAs start on the local rows and wait (bounded) for a flag before a remote block.
+  //  mode 3  parameter all-gather -> GEMM (FSDP): B is one weight inside a UNIT of parameters whose 16-bit bytes are sharded
+  //          evenly over the ranks (symmetric "wire" buffers). The first `gather_ctas` CTAs copy every rank's shard of the
+  //          whole unit into the local unsharded buffer chunk by chunk, the chunks that hold B first, and publish a flag
+  //          per chunk; the producer of a compute CTA waits (bounded) for the chunks under its B tile. When the kernel
+  //          ends the whole unit is local, so the block's other linears just read it.
   int mode, world, rank, mblocks_per_rank, gather_ctas;
+  long long g_src_off, g_per_bytes, g_b_off;  // mode 3: shard offset in the wire buffers, bytes per rank, offset of B in the unit
+  uint8_t* g_dst;                             // mode 3: local unsharded unit buffer
+  int g_chunk_bytes, g_chunks_per_rank;       // mode 3: copy / flag granularity
   uint32_t epoch;
   uint32_t* local_flags;  // device uint32: [0] go flag, [1] finished-CTA counter, [2 + m_blk] m-block ready flags
   long long a_row_bytes;  // mode 2: bytes of one row of A (rows are contiguous)
@@ -135,7 +143,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int items = p.m_blocks * p.n_blocks * p.k_splits;
   int fail_role = 0, fail_item = -1;
   // compute CTAs: index cta0 of nctas (in mode 2 the first gather_ctas CTAs only move data)
-  const int first_compute = p.mode == 2 ? p.gather_ctas : 0;
+  const int first_compute = (p.mode == 2 || p.mode == 3) ? p.gather_ctas : 0;
   const int cta0 = (int)blockIdx.x - first_compute, nctas = (int)gridDim.x - first_compute;
   // m-block visited at position `ord`: mode 2 starts with this rank's own rows, then follows the gather order
   auto m_of = [&](int ord) { return p.mode == 2 ? (p.rank * p.mblocks_per_rank + ord) % p.m_blocks : ord; };
@@ -155,7 +163,81 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) nnbcomm::st_release_gpu(p.local_flags, ok ? p.epoch : p.epoch - 1);
   }
 
-  if (p.mode == 2 && cta0 < 0) {
+  if (p.mode == 3 && cta0 < 0) {
+    // ------------------------------------------------------------------ unit gather CTAs (FSDP parameter all-gather)
+    const int G = p.gather_ctas, me = blockIdx.x;
+    bool ok = nnbcomm::block_barrier(p.peers, p.rank, p.world, 0, me, G, p.epoch, p.comm_status);  // every rank's shard is final
+    // chunk id = r * chunks_per_rank + k covers bytes [k CB, min((k + 1) CB, per)) of rank r's shard. This CTA copies the
+    // chunks with id % G == me: first the ones that intersect B (the GEMM is waiting for those), then the others.
+    uint16_t* my_chunks = reinterpret_cast<uint16_t*>(staging);   // staging tiles are unused by a gather CTA
+    __shared__ int s_total;
+    const long long CB = p.g_chunk_bytes, per = p.g_per_bytes;
+    const long long b0 = p.g_b_off, b1 = p.g_b_off + (long long)p.N * p.K * 2;
+    if (threadIdx.x == 0) {
+      int n = 0;
+      const int total_chunks = p.world * p.g_chunks_per_rank;
+      for (int pass = 0; pass < 2; ++pass)
+        for (int step = 0; step < p.world; ++step) {
+          const int r = (p.rank + step) % p.world;  // own shard first, then the peers in ring order
+          for (int k = 0; k < p.g_chunks_per_rank; ++k) {
+            const int id = r * p.g_chunks_per_rank + k;
+            if (id % G != me || id >= total_chunks) continue;
+            const long long c0 = (long long)r * per + k * CB, c1 = min(c0 + CB, (long long)(r + 1) * per);
+            const bool in_b = c0 < b1 && c1 > b0;
+            if (in_b == (pass == 0) && n < (int)(kStagingBytes / 2)) my_chunks[n++] = (uint16_t)id;
+          }
+        }
+      s_total = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && ok) {
+      const int total = s_total;
+      constexpr int S = C::kStages;
+      constexpr int kLag = 2;
+      auto locate = [&](int i, long long& src_off, long long& dst_off, uint32_t& bytes, int& r) {
+        const int id = my_chunks[i];
+        r = id / p.g_chunks_per_rank;
+        const long long k = id % p.g_chunks_per_rank;
+        bytes = (uint32_t)min(CB, per - k * CB);
+        src_off = p.g_src_off + k * CB;
+        dst_off = (long long)r * per + k * CB;
+      };
+      auto publish = [&](int j) {
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        nnbcomm::st_release_gpu(p.local_flags + 2 + my_chunks[j], p.epoch);
+      };
+      for (int i = 0; i < total + (S - kLag) && ok; ++i) {
+        if (i < total) {
+          long long so, d_o; uint32_t bytes; int r;
+          locate(i, so, d_o, bytes, r);
+          const uint32_t st = i % S;
+          mbar_expect_tx(bar_full + 8 * st, bytes);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(stage_base + st * C::kStageBytes)), "l"(static_cast<const uint8_t*>(p.peers.data[r]) + so),
+                         "r"(bytes), "r"(bar_full + 8 * st) : "memory");
+        }
+        const int j = i - (S - kLag);
+        if (j >= 0 && j < total) {
+          long long so, d_o; uint32_t bytes; int r;
+          locate(j, so, d_o, bytes, r);
+          const uint32_t st = j % S;
+          if (!mbar_wait(bar_full + 8 * st, (j / S) & 1, abort_flag)) { ok = false; break; }
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(p.g_dst + d_o),
+                       "r"(smem_u32(stage_base + st * C::kStageBytes)), "r"(bytes) : "memory");
+          tma_commit_group();
+          tma_wait_group<kLag - 1>();  // the stage the next load overwrites has been read; everything older is complete in memory
+          if (j - (kLag - 1) >= 0) publish(j - (kLag - 1));
+        }
+      }
+      tma_wait_group<0>();
+      if (ok)
+        for (int j = max(0, total - (kLag - 1)); j < total; ++j) publish(j);
+    }
+    __syncthreads();
+    // this rank's shard may be rewritten (by the optimizer) only after every peer has copied it
+    nnbcomm::block_barrier(p.peers, p.rank, p.world, 1, me, G, p.epoch, p.comm_status);
+  } else if (p.mode == 2 && cta0 < 0) {
     // ------------------------------------------------------------------ gather CTAs (all threads copy)
     const int G = p.gather_ctas, me = blockIdx.x;
     bool ok = nnbcomm::block_barrier(p.peers, p.rank, p.world, 0, me, G, p.epoch, p.comm_status);  // peers' shards are final
@@ -246,6 +328,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of the gather CTAs -> TMA reads
+        }
+        if (p.mode == 3) {
+          // rows [n0, n1) of B are bytes [x0, x1) of the unit: wait for every chunk under them
+          const long long row_bytes = (long long)p.K * 2;
+          long long x = p.g_b_off + (long long)n_blk * BN * row_bytes;
+          const long long x1 = p.g_b_off + (long long)min((n_blk + 1) * BN, p.N) * row_bytes;
+          while (x < x1 && ok) {
+            const long long r = x / p.g_per_bytes, k = (x - r * p.g_per_bytes) / p.g_chunk_bytes;
+            const uint32_t* flag = p.local_flags + 2 + r * p.g_chunks_per_rank + k;
+            nnbcomm::Deadline dl;
+            while ((int32_t)(nnbcomm::ld_acquire_gpu(flag) - p.epoch) < 0) {
+              if (dl.expired() || *abort_flag) { ok = false; *abort_flag = 1; fail_role = 4; fail_item = item; break; }
+              __nanosleep(32);
+            }
+            x = min((r + 1) * p.g_per_bytes, r * p.g_per_bytes + (k + 1) * (long long)p.g_chunk_bytes);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // bulk-copy writes of the gather CTAs -> TMA reads
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
@@ -474,6 +574,10 @@ struct CommArgs {           // mode 0 when null
   void* local_flags;        // device uint32 [2 + m_blocks], zero before the first call
   void* comm_status;        // device int[8]
   int epoch;
+  // mode 3 (data_ptrs = every rank's wire buffer): the unit's shard starts at src_off bytes in each of them and is per_bytes
+  // long; dst = local unsharded unit buffer; B sits b_off bytes into the unit
+  long long src_off = 0, per_bytes = 0, b_off = 0;
+  void* dst = nullptr;
 };
 
 int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn,
@@ -579,12 +683,23 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   if (mode != 0) {
     p.world = comm->world; p.rank = comm->rank;
     p.mblocks_per_rank = p.m_blocks / comm->world;
-    p.gather_ctas = mode == 2 ? comm->gather_ctas : 0;
+    p.gather_ctas = (mode == 2 || mode == 3) ? comm->gather_ctas : 0;
     p.epoch = (uint32_t)comm->epoch;
     p.local_flags = static_cast<uint32_t*>(comm->local_flags);
     p.comm_status = static_cast<int*>(comm->comm_status);
     p.a_row_bytes = lda * 2;
-    if (nnbcomm::fill_peers(p.peers, mode == 2 ? comm->data_ptrs : nullptr, comm->flag_ptrs, comm->world) != 0) return -1;
+    if (nnbcomm::fill_peers(p.peers, (mode == 2 || mode == 3) ? comm->data_ptrs : nullptr, comm->flag_ptrs, comm->world) != 0) return -1;
+    if (mode == 3) {
+      NNB_REQUIRE(!a_mn && !b_mn && ldb == K, "gather_b_gemm: K-major operands with a contiguous weight expected");
+      NNB_REQUIRE(comm->gather_ctas >= 1 && comm->gather_ctas < sms, "gather_b_gemm: bad gather CTA count %d", comm->gather_ctas);
+      NNB_REQUIRE(comm->per_bytes > 0 && comm->per_bytes % 16 == 0 && comm->src_off % 16 == 0 && nnb_aligned16(comm->dst),
+                  "gather_b_gemm: shards must be 16-byte aligned");
+      p.g_src_off = comm->src_off; p.g_per_bytes = comm->per_bytes; p.g_b_off = comm->b_off;
+      p.g_dst = static_cast<uint8_t*>(comm->dst);
+      p.g_chunk_bytes = 32768;  // fits one operand stage of every tile width; 16-byte multiple
+      p.g_chunks_per_rank = (int)((comm->per_bytes + p.g_chunk_bytes - 1) / p.g_chunk_bytes);
+      NNB_REQUIRE((long long)p.g_chunks_per_rank * comm->world <= 16000, "gather_b_gemm: unit too large for the chunk table");
+    }
     if (mode == 2) {
       NNB_REQUIRE(!a_mn && lda == K && M % (BM * comm->world) == 0, "ag_gemm: A must be contiguous [M, K] with M a multiple of %d x world", BM);
       NNB_REQUIRE(comm->gather_ctas >= 1 && comm->gather_ctas < sms, "ag_gemm: bad gather CTA count %d", comm->gather_ctas);
@@ -598,7 +713,7 @@ int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long l
   }
   const int items = p.m_blocks * p.n_blocks * p.k_splits;
   int grid = min(items, sms);
-  if (mode == 2) grid = min(items + p.gather_ctas, sms);
+  if (mode == 2 || mode == 3) grid = min(items + p.gather_ctas, sms);
   const int rc = BN == 256 ? launch<256>(tmA, tmB, tmDs, p, grid, st)
                : BN == 192 ? launch<192>(tmA, tmB, tmDs, p, grid, st) : launch<128>(tmA, tmB, tmDs, p, grid, st);
   if (rc != 0) return rc;
@@ -682,6 +797,23 @@ extern "C" int nnb_ag_gemm_bf16(void* const* a_ptrs, const void* B, void* D, voi
                                 long long ldb, long long ldd, int b_mn, int dtype, void* status, cudaStream_t st) {
   CommArgs c{2, world, rank, gather_ctas, a_ptrs, flag_ptrs, local_flags, comm_status, epoch};
   return gemm_impl(a_ptrs[rank], B, D, M, N, K, K, ldb, ldd, 0, b_mn, dtype, 0, 0, 1, 0, 0, status, &c, st);
+}
+
+// parameter all-gather -> GEMM in one kernel (first linear of an FSDP unit):
+//   D[M, N] = A[M, K] @ B[N, K]^T where B lives b_off bytes into a unit of parameters whose bytes are sharded evenly over the
+//   ranks: rank r holds bytes [r per_bytes, (r + 1) per_bytes) of the unit in ITS wire buffer at src_off. The first
+//   gather_ctas CTAs copy all shards of the WHOLE unit into unit_dst (this rank's unsharded copy), B's chunks first; the
+//   other CTAs multiply, each waiting only for the chunks under its own B tile. local_flags: device uint32
+//   [2 + world * ceil(per_bytes / 32768)], zero before the first call. After the kernel the whole unit is valid in unit_dst.
+extern "C" int nnb_gather_b_gemm_bf16(const void* A, void* const* wire_ptrs, void* unit_dst, void* D, void* const* flag_ptrs,
+                                      void* local_flags, void* comm_status, int rank, int world, int epoch, int gather_ctas,
+                                      long long src_off, long long per_bytes, long long b_off, int M, int N, int K, long long lda,
+                                      long long ldd, int dtype, void* status, cudaStream_t st) {
+  CommArgs c{3, world, rank, gather_ctas, wire_ptrs, flag_ptrs, local_flags, comm_status, epoch};
+  c.src_off = src_off; c.per_bytes = per_bytes; c.b_off = b_off; c.dst = unit_dst;
+  NNB_REQUIRE(b_off % 16 == 0 && b_off >= 0 && b_off + (long long)N * K * 2 <= per_bytes * world, "gather_b_gemm: B outside the unit");
+  const void* B = static_cast<const uint8_t*>(unit_dst) + b_off;
+  return gemm_impl(A, B, D, M, N, K, lda, K, ldd, 0, 0, dtype, 0, 0, 1, 256, 0, status, &c, st);
 }
 
 // MXFP8 GEMM on the block-scaled tensor-core path: D[M, N] (+)= (A * sfa) (B * sfb)^T.

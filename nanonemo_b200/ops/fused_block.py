@@ -44,9 +44,15 @@ class _QKVRopeAttention(torch.autograd.Function):
         x2 = _rows16(x, dt)
         cos_t, sin_t = rope._tables(cos, sin, T)
         rot_cols = (H + KVH) * hd
-        qkv = gemm_rope(x2, w16, cos_t, sin_t, T, rot_cols, hd)
-        if qkv is None:
-            qkv = gemm(x2, w16)
+        gather = getattr(weight, "_gather_in_gemm", None)
+        if gather is not None:
+            # FSDP: this GEMM kernel also all-gathers the block's parameters (the weight itself first), see parallel/fsdp.py
+            qkv = gather(x2, weight)
+        else:
+            qkv = gemm_rope(x2, w16, cos_t, sin_t, T, rot_cols, hd)
+        if qkv is None or gather is not None:
+            if qkv is None:
+                qkv = gemm(x2, w16)
             rope.rope_packed_raw(qkv, qkv, cos_t, sin_t, T, H + KVH, hd, 0, 1.0)  # rotates Q and K in place, V untouched
         qkv = qkv.view(B, T, -1)
         q, k, v = _split(qkv, B, T, H, KVH, hd)

@@ -242,6 +242,24 @@ class FusedCollectiveGemm:
                   _lib.i32(int(b_mn)), _lib.i32(_CODE[dtype]), _lib.ptr(status_tensor(b.device)), _lib.vp(_lib.stream_ptr()))
         return out
 
+    def gather_b_gemm(self, a: torch.Tensor, wire, src_off_bytes: int, per_bytes: int, unit_dst: torch.Tensor, b_off_bytes: int,
+                      N: int, out: torch.Tensor | None = None):
+        """a [M, K] @ B[N, K]^T where B sits `b_off_bytes` into a parameter unit sharded over the ranks (`wire`:
+        SymmetricBuffer with every rank's shard at `src_off_bytes`, `per_bytes` each). The kernel all-gathers the WHOLE unit
+        into `unit_dst` (this rank's unsharded 16-bit copy) while it multiplies: afterwards every parameter of the unit is local."""
+        a = _rowmajor2d(a)
+        M, K = a.shape
+        out = out if out is not None else torch.empty((M, N), dtype=a.dtype, device=a.device)
+        chunks = self.world * ((per_bytes + 32767) // 32768)
+        assert 2 + chunks <= self.local_flags.numel(), "unit too large for the flag table"
+        self.epoch += 1
+        _lib.call("nnb_gather_b_gemm_bf16", _lib.ptr(a), wire.ptr_array, _lib.ptr(unit_dst), _lib.ptr(out), self.flags.ptr_array,
+                  _lib.ptr(self.local_flags), _lib.ptr(self.comm_status), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.epoch),
+                  _lib.i32(self.gather_ctas), _lib.i64(src_off_bytes), _lib.i64(per_bytes), _lib.i64(b_off_bytes), _lib.i32(M), _lib.i32(N),
+                  _lib.i32(K), _lib.i64(a.stride(0)), _lib.i64(out.stride(0)), _lib.i32(_CODE[a.dtype]), _lib.ptr(status_tensor(a.device)),
+                  _lib.vp(_lib.stream_ptr()))
+        return out
+
     def check_status(self):
         st = self.comm_status.tolist()
         if st[0] != 0:

@@ -48,7 +48,7 @@ class FSDPStrategy(LocalStrategy):
     sharded_grads = True
 
     def __init__(self, model, d, param_dtype="fp32", reshard_after_forward=True, prefetch=False, comm="auto",
-                 group=None, step_model=None, precision="fp32"):
+                 group=None, step_model=None, precision="fp32", gemm_gather=False):
         super().__init__(model, None, step_model)
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
@@ -67,6 +67,7 @@ class FSDPStrategy(LocalStrategy):
         self._allocate()
         self._install_hooks()
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self._setup_gemm_gather(gemm_gather)
         self.sumsq = torch.zeros((), dtype=torch.float32, device=self.device)
         self._rs_done = []
         self._update_in_rs = None  # AdamW hyper-parameters of the current step when the update rides in the reduce-scatter
@@ -245,7 +246,66 @@ class FSDPStrategy(LocalStrategy):
                 p.register_post_accumulate_grad_hook(lambda p, u=u: self._on_grad(u, p, False))
                 p._grad_ready_cb = lambda p, manual=True, u=u: self._on_grad(u, p, manual)
 
+    # -- forward all-gather inside the block's QKV GEMM (fsdp_gemm_gather)
+    def _setup_gemm_gather(self, wanted: bool):
+        """With `fsdp_gemm_gather` the forward pass launches NO all-gather kernel for a block: the block's QKV projection
+        runs as the single kernel that copies the peers' shards of the whole unit in (gather CTAs, the weight's own chunks
+        first) while its other CTAs multiply, each waiting only for the chunks under its tile (csrc/gemm.cu mode 3). The one
+        parameter a block reads before that kernel, its first norm weight, is fetched for all blocks in one small launch
+        right after the optimizer step. Needs the fused collectives, 16-bit gathered parameters and the sm100 attention path."""
+        self.fg = None
+        self._gg_norm_items = None
+        if not (wanted and self.fused and self.param_dtype != torch.float32 and type(self) is FSDPStrategy):
+            return
+        blocks = [u for u in self.units[1:]]
+        if not all(getattr(u.modules[0].attn, "fused", False) and u.names[0].endswith("norm_attn.weight")
+                   and u.names[1].endswith("attn.wqkv.weight") for u in blocks):
+            return
+        from nanonemo_b200.ops.gemm import FusedCollectiveGemm
+
+        self.fg = FusedCollectiveGemm(self.device, self.group, self.rank, self.world)
+        esz = self.wire.element_size()
+        rows = []
+        for u in blocks:
+            s0, _ = self._shard_range(u)
+            n = _round_up(u.params[0].numel(), ALIGN) * esz           # the norm weight opens the unit: it is in rank 0's shard
+            assert n <= (u.hi - u.lo) // self.world * esz
+            rows.append([s0 * esz, n, self.full.data_ptr() + u.lo * esz, 0])
+        self._gg_norm_items = torch.tensor(rows, dtype=torch.int64, device=self.device)
+
+    def _fetch_first_norms(self):
+        """One launch: every block's first norm weight from the rank that owns it (after the shards were updated)."""
+        if self._gg_norm_items is None:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self.comm_stream.wait_event(ev)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm.peer_fetch(self.symm_wire, self._gg_norm_items, self._gg_norm_items.shape[0])
+            done = torch.cuda.Event()
+            done.record()
+        self._gg_norms_event = done
+        self.launches += 1
+
+    def _qkv_gemm_with_gather(self, u, x2, weight):
+        """Called by the attention operator in place of its QKV GEMM: all-gathers unit `u` inside the GEMM kernel."""
+        esz = self.wire.element_size()
+        s0, s1 = self._shard_range(u)
+        unit = self.full[u.lo:u.hi]
+        out = self.fg.gather_b_gemm(x2, self.symm_wire, s0 * esz, (s1 - s0) * esz, unit, u.offsets[1] * esz, weight.shape[0])
+        u.gathered, u.gather_event = True, None
+        del weight._gather_in_gemm
+        self.launches += 1
+        return out
+
     def _pre_forward(self, i):
+        u = self.units[i]
+        if self.fg is not None and not u.gathered and u.gather_event is None and torch.is_grad_enabled():
+            ev = self.__dict__.pop("_gg_norms_event", None)
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+            u.params[1]._gather_in_gemm = lambda x2, w, u=u: self._qkv_gemm_with_gather(u, x2, w)
+            return
         self._wait_gather(self.units[i])
         if self.prefetch and i + 1 < len(self.units) and not self.units[i + 1].gathered:
             self._gather(self.units[i + 1])
@@ -277,8 +337,8 @@ class FSDPStrategy(LocalStrategy):
         if not self.units[0].gathered:
             self._gather(self.units[0])
         self._wait_gather(self.units[0])
-        if self.prefetch and not self.units[1].gathered:
-            self._gather(self.units[1])
+        if self.prefetch and self.fg is None and not self.units[1].gathered:
+            self._gather(self.units[1])  # (with fsdp_gemm_gather the first block gathers itself inside its QKV GEMM)
         return nullcontext()
 
     def begin_step(self, opt, grad_clip) -> None:
@@ -380,6 +440,7 @@ class FSDPStrategy(LocalStrategy):
             u.gathered = False
         # the root and (with prefetch) the first block are needed at once: start gathering now
         self._gather(self.units[0])
+        self._fetch_first_norms()
         return norm
 
     # ------------------------------------------------------------------ checkpoint state (streamed, one unit at a time)
@@ -502,4 +563,4 @@ def build_fsdp(model_cfg, cfg, d):
     if pd == "fp32" and model_cfg.uses_sm100("linear_impl") and cfg.precision in ("bf16", "fp8"):
         pd = "bf16"  # the tensor-core GEMMs consume 16-bit weights: gather them in that dtype
     return FSDPStrategy(model, d, pd, cfg.fsdp_reshard_after_forward, cfg.fsdp_prefetch, cfg.comm,
-                        step_model=step_model, precision=cfg.precision)
+                        step_model=step_model, precision=cfg.precision, gemm_gather=cfg.fsdp_gemm_gather)

@@ -146,6 +146,15 @@ class SymmetricComm:
                   _lib.i64(per_bytes), _lib.i32(self.blocks), ctypes.c_double(self.timeout_s),
                   ctypes.c_void_p(_lib.stream_ptr()))
 
+    def peer_fetch(self, data: "SymmetricBuffer", items: torch.Tensor, n_items: int):
+        """One launch copies `n_items` small ranges from the ranks that own them into local memory. `items`: device int64
+        [n_items, 4] rows (src_off bytes, bytes, destination address, src_rank); everything 16-byte aligned."""
+        from nanonemo_b200.ops import _lib
+
+        _lib.call("nnb_peer_fetch", data.ptr_array, self.flags.ptr_array, _lib.ptr(items), _lib.i32(n_items), _lib.ptr(self.status),
+                  _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.blocks),
+                  ctypes.c_double(self.timeout_s), ctypes.c_void_p(_lib.stream_ptr()))
+
     def check_status(self):
         st = self.status.tolist()
         if st[0] != 0:

@@ -58,6 +58,7 @@ class TrainConfig:
     tp_size: int | None = None  # tensor-parallel degree for parallel=tp (default: world) / fsdp_tp
     comm: str = "auto"  # auto | fused | nccl
     residual_dtype: str = "fp32"  # dtype of the residual stream on the sm100 path: fp32 | bf16
+    fsdp_gemm_gather: bool = False  # fsdp forward: a block's parameter all-gather runs inside its QKV GEMM kernel (no side-stream gather)
     cuda_graph: bool = False  # replay forward + backward (+ the ddp gradient all-reduce) of a micro-batch from a CUDA graph
 
     def __post_init__(self):

@@ -110,7 +110,8 @@ def main():
     say(f"COLLECTIVES world={world}: {'ok' if ok else 'MISMATCH'}")
     single = run_layout(d, "none", fake_single=True)
     say("single-GPU losses:", [round(x, 4) for x in single])
-    layouts = [("ddp", {}), ("ddp+graph", {"parallel": "ddp", "cuda_graph": True}), ("fsdp", {}), ("tp", {})]
+    layouts = [("ddp", {}), ("ddp+graph", {"parallel": "ddp", "cuda_graph": True}), ("fsdp", {}),
+               ("fsdp, all-gather inside the QKV GEMM", {"parallel": "fsdp", "fsdp_gemm_gather": True}), ("tp", {})]
     if world >= 4:
         layouts.append(("fsdp_tp", {"tp_size": 2}))
     for name, extra in layouts:
