@@ -1,7 +1,8 @@
 """Small profiler target: a few launches of one kernel family at a shape larger than L2 but holding only
 a few hundred MB, so an `ncu --set full` capture ends by itself in about a minute.
 
-    python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,flash,flash128,rmsnorm,swiglu,rope,ce,adamw} [iters]
+    python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,gemm_swiglu,gemm_rope,flash,flash128,rmsnorm,swiglu,rope,
+                                             ce,adamw,embedding,quantize} [iters]
 """
 
 import sys
@@ -35,6 +36,27 @@ def main():
         aq, asf, _, _ = fp8.quantize_mx(torch.randn(M, 768, device=dev, dtype=bf))
         bq, bsf, _, _ = fp8.quantize_mx(torch.randn(4096, 768, device=dev, dtype=bf))
         fn = lambda: fp8.gemm_mxfp8(aq, asf, bq, bsf)
+    elif kind == "gemm_swiglu":
+        from nanonemo_b200.ops.gemm import gemm_swiglu
+
+        a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(4096, 768, device=dev, dtype=bf)
+        fn = lambda: gemm_swiglu(a, b)  # gate||up projection with the SwiGLU epilogue (gemm2_tcgen05_kernel<1>)
+    elif kind == "gemm_rope":
+        from nanonemo_b200.models.layers import rope_cache
+        from nanonemo_b200.ops.gemm import gemm_rope
+
+        cos, sin = (t.contiguous() for t in rope_cache(64, 1024, device=dev))
+        a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(1280, 768, device=dev, dtype=bf)
+        fn = lambda: gemm_rope(a, b, cos, sin, 1024, 1024, 64)  # QKV projection with the RoPE epilogue (gemm2_tcgen05_kernel<2>)
+    elif kind == "embedding":
+        idx = torch.randint(0, 50257, (M,), device=dev)
+        w = (torch.randn(50304, 768, device=dev) * 0.02).requires_grad_()
+        fn = lambda: ops.embedding(idx, w, impl="sm100").sum().backward()
+    elif kind == "quantize":
+        from nanonemo_b200 import fp8
+
+        x = torch.randn(M, 2048, device=dev, dtype=bf)
+        fn = lambda: fp8.quantize_mx(x, True, True)  # one read -> row-wise e4m3 copy + transposed copy + both scale sets
     elif kind == "flash128":
         qkv = torch.randn(4, 2048, 24 * 128, device=dev, dtype=bf, requires_grad=True)
         fn = lambda: ops.attention_packed(qkv, 16, 4, 128, impl="sm100").sum().backward()

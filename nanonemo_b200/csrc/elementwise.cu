@@ -54,15 +54,17 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TX* __restri
 }
 
 // n = h*rstd, dn = dy*w, dh = rstd*(dn - n*mean(dn*n)) + dres; dx = ddelta = dh; dw = sum_rows dy*n.
-// Persistent: each warp strides over rows; the norm weight and a per-warp dw accumulator live in
-// shared memory (so the register file only holds one row), warps of a block are then summed and the
-// block writes one partial row of dw, reduced in index order by dw_reduce_kernel.
+// Persistent: each warp strides over rows; the norm weight and a per-warp dw accumulator live in shared memory (so the
+// register file only holds one row), warps of a block are then summed and the block writes one partial row of dw, reduced in
+// index order by dw_reduce_kernel. Every load of a row (h, dy AND the incoming residual gradient) is issued before the first
+// use, so a warp has its whole ~8 KB in flight at once instead of paying the memory latency twice per row, and blocks are
+// 128 threads with at most 128 registers so that four of them (16 warps) share an SM.
 template <typename TX, typename TD, typename TY, int MAXC>
-__global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ h,
-                                                              const float* __restrict__ rstd,
-                                                              const float* __restrict__ w, const TX* __restrict__ dres,
-                                                              TX* __restrict__ dx, TD* __restrict__ ddelta,
-                                                              float* __restrict__ dw_partial, int M, int N) {
+__global__ void __launch_bounds__(128, MAXC <= 4 ? 4 : 2) add_rmsnorm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ h,
+                                                                 const float* __restrict__ rstd,
+                                                                 const float* __restrict__ w, const TX* __restrict__ dres,
+                                                                 TX* __restrict__ dx, TD* __restrict__ ddelta,
+                                                                 float* __restrict__ dw_partial, int M, int N) {
   extern __shared__ float s_mem[];  // [N] weight, then [warps][N] accumulators
   const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5, warps_per_block = blockDim.x >> 5;
   const int nchunks = N >> 3;
@@ -74,15 +76,25 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TY* __restri
   const float inv_n = 1.f / (float)N;
   for (int row = blockIdx.x * warps_per_block + warp_in_block; row < M; row += gridDim.x * warps_per_block) {
     const size_t base = (size_t)row * N;
-    const float r = rstd[row];
-    float n_[MAXC][8], dn[MAXC][8];
-    float dot = 0.f;
+    constexpr bool kEarly = MAXC <= 4;  // wider rows (N up to 2048) would spill: they fetch the residual gradient late
+    float n_[MAXC][8], dn[MAXC][8], res[kEarly ? MAXC : 1][8];
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = lane + 32 * c;
       if (ch < nchunks) {
         Chunk8<TX>::load(h + base + ch * 8, n_[c]);
         Chunk8<TY>::load(dy + base + ch * 8, dn[c]);
+        if constexpr (kEarly) {
+          if (dres != nullptr) Chunk8<TX>::load(dres + base + ch * 8, res[c]);
+        }
+      }
+    }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < nchunks) {
         float g[8], a[8];
         Chunk8<float>::load(s_w + ch * 8, g);
         Chunk8<float>::load(s_acc + ch * 8, a);
@@ -102,9 +114,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TY* __restri
       const int ch = lane + 32 * c;
       if (ch < nchunks) {
         float o[8];
-        if (dres != nullptr) Chunk8<TX>::load(dres + base + ch * 8, o);
+        if constexpr (!kEarly) {
+          if (dres != nullptr) Chunk8<TX>::load(dres + base + ch * 8, res[0]);
+        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = r * (dn[c][i] - n_[c][i] * dot) + (dres != nullptr ? o[i] : 0.f);
+        for (int i = 0; i < 8; ++i) o[i] = r * (dn[c][i] - n_[c][i] * dot) + (dres != nullptr ? res[kEarly ? c : 0][i] : 0.f);
         Chunk8<TX>::store(dx + base + ch * 8, o);
         if (ddelta != nullptr) Chunk8<TD>::store(ddelta + base + ch * 8, o);
       }
@@ -180,17 +194,17 @@ extern "C" int nnb_add_rmsnorm_fwd(const void* x, const void* delta, const void*
   return 0;
 }
 
-extern "C" int nnb_rmsnorm_bwd_blocks() { return 4 * nnb_num_sms(); }
+extern "C" int nnb_rmsnorm_bwd_blocks() { return 4 * nnb_num_sms(); }  // four 128-thread blocks per SM, persistent
 
 template <typename TX, typename TD, typename TY>
 static int rmsnorm_bwd_t(const void* dy, const void* h, const float* rstd, const float* w, const void* dres, void* dx,
                          void* ddelta, float* partial, int blocks, int M, int N, cudaStream_t st) {
-  const size_t smem = (size_t)N * 9 * sizeof(float);
+  const size_t smem = (size_t)N * 5 * sizeof(float);  // the weight + one accumulator row per warp (4 warps)
 #define NNB_RMS_BWD(MAXC)                                                                                         \
   {                                                                                                               \
     auto k = add_rmsnorm_bwd_kernel<TX, TD, TY, MAXC>;                                                            \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -3; \
-    k<<<blocks, 256, smem, st>>>((const TY*)dy, (const TX*)h, rstd, w, (const TX*)dres, (TX*)dx, (TD*)ddelta, partial, M, N); \
+    k<<<blocks, 128, smem, st>>>((const TY*)dy, (const TX*)h, rstd, w, (const TX*)dres, (TX*)dx, (TD*)ddelta, partial, M, N); \
   }
   if (N <= 768) NNB_RMS_BWD(3)   // one row fits 3 chunks per lane: fewer registers, more resident warps
   else if (N <= 1024) NNB_RMS_BWD(4)
@@ -204,7 +218,7 @@ extern "C" int nnb_add_rmsnorm_bwd(const void* dy, const void* h, const void* rs
                                    void* dx, void* ddelta, void* dw, void* dw_partial, int M, int N, int x_dtype,
                                    int delta_dtype, int y_dtype, int accumulate_dw, cudaStream_t st) {
   NNB_REQUIRE(N % 8 == 0 && N <= 2048 && N > 0, "add_rmsnorm_bwd: N=%d must be a multiple of 8 and <= 2048", N);
-  const int blocks = min(nnb_rmsnorm_bwd_blocks(), (M + 7) / 8);
+  const int blocks = min(nnb_rmsnorm_bwd_blocks(), (M + 3) / 4);
   bool done = false;
   int rc = 0;
 #define X(cx, cd, cy, TX, TD, TY)                                                                      \

@@ -103,7 +103,7 @@ class Attention(nn.Module):
         if self.tp is not None:
             # sequence parallel: x holds 1/tp of the tokens; gather them, attend over the local heads,
             # and reduce-scatter the row-parallel projection's partial sums back to token shards
-            if self.tp.fused_tp is not None:
+            if self.tp.fused_tp is not None and self.tp.pair == 1:
                 from nanonemo_b200.parallel.tp_fused import column_parallel_linear, row_parallel_linear
 
                 ft = self.tp.fused_tp  # the gather and the scatter happen inside the two GEMM kernels

@@ -4,10 +4,11 @@
 asking for ``sm100`` without the built library, or off a CUDA device, raises.
 
 The sm100 kernels are bound once, as ``torch.library`` custom operators with fake implementations and autograd
-formulas (``ops/library.py``), and that is what these functions call. The one exception is a parameter that lives in
-the trainer's flat parameter store (it carries ``_main_grad``): its operators run as ``autograd.Function``s that
-accumulate the weight gradient in place in the flat fp32 buffer and tell the strategy when it is complete — what a
-functional operator may not do. Both routes launch the same kernels.
+formulas (``ops/library.py``), and that is what these functions call. The exception is the trainer's engine: a
+parameter that lives in a flat parameter store (it carries ``_main_grad``) runs its operators as ``autograd.Function``s
+that accumulate the weight gradient in place in the flat fp32 buffer and tell the strategy when it is complete — what a
+functional operator may not do — and once such a store exists the weightless operators take the direct functions of
+``ops/direct.py`` too (no dispatcher round trip on the hot path). Both routes launch the same kernels.
 
 Operator contracts follow the reference kernels (nanonemo/kernels/triton/*.py,
 nanonemo/kernels/cuda/*.py): ``add_rms_norm(x, delta, w, eps) -> (y, h)``, RoPE on Q and K in one
@@ -20,10 +21,15 @@ from torch.nn.attention import SDPBackend, sdpa_kernel
 
 
 # ----------------------------------------------------------------------------- torch oracles
+def _wide(x: torch.Tensor) -> torch.Tensor:
+    """The dtype the oracles do their arithmetic in: fp32, or fp64 for fp64 inputs (gradcheck)."""
+    return x if x.dtype == torch.float64 else x.float()
+
+
 def rms_norm_torch(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
+    xf = _wide(x)
     xf = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
-    return (xf * weight.float()).to(x.dtype)
+    return (xf * weight.to(xf.dtype)).to(x.dtype)
 
 
 def add_rms_norm_torch(x, delta, weight, eps):
@@ -39,7 +45,7 @@ def rope_torch(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_dim: i
     cos, sin = cos[:T], sin[:T]
     if seq_dim in (1, -3):
         cos, sin = cos[:, None, :], sin[:, None, :]
-    xf = x.float()
+    xf = _wide(x)
     x1, x2 = xf[..., :half], xf[..., half:]
     return torch.cat((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).to(x.dtype)
 
@@ -59,7 +65,7 @@ def swiglu_torch(g, u):
 
 
 def linear_cross_entropy_torch(x, weight, targets):
-    return F.cross_entropy(F.linear(x, weight).float(), targets)
+    return F.cross_entropy(_wide(F.linear(x, weight)), targets)
 
 
 # ----------------------------------------------------------------------------- dispatch
@@ -119,10 +125,12 @@ def rope_qkv(qkv, cos, sin, n_heads, n_kv_heads, head_dim, impl="torch"):
         k = rope_torch(k.reshape(B, T, n_kv_heads, head_dim), cos, sin, seq_dim=1).reshape(B, T, kd)
         return torch.cat((q, k, v), dim=-1)
     _need_cuda(qkv, "rope_qkv")
-    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops import direct, library
     from nanonemo_b200.ops.rope import _tables
 
     c, s = _tables(cos, sin, qkv.shape[1])
+    if direct.ENABLED:
+        return direct.rope_qkv(qkv, c, s, n_heads, n_kv_heads, head_dim)
     return library.rope_qkv(qkv, c, s, n_heads, n_kv_heads, head_dim)
 
 
@@ -153,8 +161,10 @@ def attention_packed(qkv, n_heads, n_kv_heads, head_dim, impl="torch", backend=S
         v = v.view(B, T, n_kv_heads, head_dim).transpose(1, 2)
         return attention_torch(q, k, v, backend).transpose(1, 2).reshape(B, T, qd)
     _need_cuda(qkv, "attention_packed")
-    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops import direct, library
 
+    if direct.ENABLED and qkv.dtype == torch.bfloat16:
+        return direct.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)
     if qkv.dtype != torch.bfloat16:  # the attention kernels are bf16: fp16 / fp32 inputs are converted and the result converted back
         return library.flash_attn_packed(qkv.to(torch.bfloat16), n_heads, n_kv_heads, head_dim)[0].to(qkv.dtype)
     return library.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)[0]
@@ -186,9 +196,9 @@ def swiglu_packed(gu, impl="torch"):
         g, u = gu.chunk(2, dim=-1)
         return swiglu_torch(g, u)
     _need_cuda(gu, "swiglu_packed")
-    from nanonemo_b200.ops import library
+    from nanonemo_b200.ops import direct, library
 
-    return library.swiglu(gu)
+    return direct.swiglu_packed(gu) if direct.ENABLED else library.swiglu(gu)
 
 
 def fused_ok() -> bool:

@@ -39,6 +39,10 @@ class FlatParams:
         self.params = [p for _, p in named]
         device = torch.device(device) if device is not None else self.params[0].device
         self.device = device
+        if device.type == "cuda":
+            from nanonemo_b200.ops import direct
+
+            direct.enable()  # a trainer engine owns this model: weightless operators skip the dispatcher (ops/direct.py)
         self.offsets, off = [], 0
         for p in self.params:
             self.offsets.append(off)

@@ -63,6 +63,10 @@ class FSDPStrategy(LocalStrategy):
         from nanonemo_b200.parallel.symm import fused_available
 
         self.fused = fused_available(d, comm)
+        if self.cuda:
+            from nanonemo_b200.ops import direct
+
+            direct.enable()  # trainer engine: weightless operators skip the dispatcher (ops/direct.py)
         self._build_units()
         self._allocate()
         self._install_hooks()

@@ -71,8 +71,17 @@ class LocalStrategy:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0, own0 = _lib.LAUNCHES, self.launches
-        with torch.cuda.graph(graph):
-            st["loss"] = run(st["x"], st["y"])
+        try:
+            with torch.cuda.graph(graph):
+                st["loss"] = run(st["x"], st["y"])
+        except Exception as e:  # noqa: BLE001 - capture records without executing, so nothing was computed yet: run eagerly from now on
+            import warnings
+
+            warnings.warn(f"CUDA-graph capture of the micro-batch failed ({type(e).__name__}: {str(e)[:200]}); continuing without graphs")
+            torch.cuda.synchronize()
+            self.use_cuda_graph = False
+            graphs.clear()
+            return run(x, y)
         st["launches"], st["own_launches"] = _lib.LAUNCHES - n0, self.launches - own0
         st["graph"] = graph
         graph.replay()  # capturing records the work without running it: run this micro-batch now

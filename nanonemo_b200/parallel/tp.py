@@ -354,8 +354,8 @@ def _maybe_fuse(tp, model_cfg, cfg, d, group):
     from nanonemo_b200.parallel.symm import fused_available
 
     tokens = cfg.micro_batch * cfg.seq_len
-    if tp.pair > 1:
-        return  # the pair split runs attention through the unfused gather / scatter path
+    # (under the rank-pair layout only the MLP uses the fused linears: the pair split of attention gathers the whole sequence
+    # and scatters half-empty rows, which the unfused path handles; see models/layers.py)
     if (fused_available(d, cfg.comm) and model_cfg.resolved().linear_impl == "sm100" and cfg.precision in ("bf16", "fp16")
             and tokens % (128 * tp.world) == 0):
         from nanonemo_b200.parallel.tp_fused import FusedTP

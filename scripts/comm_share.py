@@ -9,7 +9,7 @@ NCCL kernels plus this framework's collective kernels (allreduce_f32 / reduce_sc
 import csv
 import sys
 
-COMM = ("nccl", "allreduce_f32_kernel", "reduce_scatter_f32_kernel", "allgather_kernel")
+COMM = ("nccl", "allreduce_f32_kernel", "reduce_scatter_f32_kernel", "allgather_kernel", "peer_fetch_kernel")
 
 
 def main(argv=None):

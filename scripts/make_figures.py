@@ -1,11 +1,13 @@
 #!/usr/bin/env python
 """Regenerate tables (and, when matplotlib is installed, figures) from results/ only — nothing is re-measured.
 
-    python scripts/make_figures.py [--results results] [--out figures]
+    python scripts/make_figures.py [--results results] [--out figures] [--readme README.md]
 
 Tables: the optimisation ladder (results/ladder/<gpu>/*.json), the multi-GPU table (results/dist/<gpu>-xN/*.json),
 kernel micro-benchmarks (results/kernels/*.json). Figures: ladder tokens/s bar chart and, if a run's
-metrics.jsonl is given with --metrics, its loss curve.
+metrics.jsonl is given with --metrics, its loss curve. With --readme the tables also replace whatever stands between the
+``<!-- results:begin -->`` and ``<!-- results:end -->`` markers of that file (the reference regenerates the numbers block
+of its README the same way, scripts/make_figures.py:207-235), so the README never carries a hand-copied number.
 """
 
 import argparse
@@ -29,11 +31,28 @@ def dist_rows(results: Path):
             yield folder.name, name, r["tokens_per_s"]["median"], r["bench"]["world"]
 
 
+BEGIN, END = "<!-- results:begin -->", "<!-- results:end -->"
+
+
+def update_block(readme: Path, lines: list[str]) -> None:
+    """Replace the text between the two markers of `readme` with `lines` (the markers are appended if the file has none)."""
+    text = readme.read_text() if readme.exists() else ""
+    block = BEGIN + "\n" + "\n".join(lines) + "\n" + END
+    if BEGIN in text and END in text:
+        head, rest = text.split(BEGIN, 1)
+        text = head + block + rest.split(END, 1)[1]
+    else:
+        text = text.rstrip("\n") + "\n\n" + block + "\n"
+    readme.write_text(text)
+    print(f"rewrote the results block of {readme}")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--results", type=Path, default=Path("results"))
     ap.add_argument("--out", type=Path, default=Path("figures"))
     ap.add_argument("--metrics", type=Path, default=None, help="a run's metrics.jsonl for the loss curve")
+    ap.add_argument("--readme", type=Path, default=None, help="file whose results block (between the markers) is rewritten")
     a = ap.parse_args(argv)
     a.out.mkdir(parents=True, exist_ok=True)
     lines = ["## Optimisation ladder", "| gpu | stage | tok/s | step ms |", "|---|---|---|---|"]
@@ -51,6 +70,8 @@ def main(argv=None):
                 lines += ["| " + " | ".join(f"{row[k]:.4g}" if isinstance(row[k], float) else str(row[k]) for k in keys) + " |" for row in r["rows"]]
     (a.out / "tables.md").write_text("\n".join(lines) + "\n")
     print(f"wrote {a.out / 'tables.md'}")
+    if a.readme is not None:
+        update_block(a.readme, lines)
     try:
         import matplotlib
 

@@ -97,7 +97,9 @@ def test_whole_model_compiles_fullgraph_on_the_registered_operators():
     graph break anywhere) and the traced module gives the eager loss and gradients."""
     from nanonemo_b200.models.config import ModelConfig
     from nanonemo_b200.models.model import NanoNemo
+    from nanonemo_b200.ops import direct
 
+    direct.enable(False)  # (an earlier test of this process may have built a trainer engine, which switches the direct functions on)
     torch.manual_seed(0)
     model = NanoNemo(ModelConfig.sm100(**SMALL)).to(DEV)
     idx = torch.randint(0, 50257, (4, 257), device=DEV)

@@ -25,6 +25,14 @@ def test_tables_from_results_only(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     text = (out / "tables.md").read_text()
     assert "| b200 | s0_fp32 | 1,000 | 16.00 |" in text and "| b200-x2 | ddp | 5,000 | 2 |" in text and "| qkv | 0.1 |" in text
+    # the README block between the markers is regenerated from the same tables, text around it is kept
+    readme = tmp_path / "README.md"
+    readme.write_text("intro\n<!-- results:begin -->\nstale number 123\n<!-- results:end -->\noutro\n")
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "make_figures.py"), "--results", str(tmp_path / "results"), "--out", str(out),
+                        "--readme", str(readme)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    new = readme.read_text()
+    assert new.startswith("intro\n") and new.endswith("outro\n") and "stale number" not in new and "| b200 | s1_fp16 | 2,000 | 8.00 |" in new
 
 
 def test_nvtx_spans_are_noops_without_cuda(monkeypatch):
