@@ -143,7 +143,7 @@ static __device__ __align__(256) float g_sumsq_noalloc_scratch[NNB_SUMSQ_NOALLOC
 extern "C" int nnb_sumsq_f32_noalloc(const void* x, long long n, void* out, cudaStream_t st) {
   constexpr int kMaxDevices = 64;
   static float* scratch_of[kMaxDevices] = {nullptr};
-  NNB_REQUIRE(x != nullptr && out != nullptr, "sumsq_noalloc: null pointer");
+  NNB_REQUIRE(out != nullptr && (x != nullptr || n == 0), "sumsq_noalloc: null pointer");  // an empty input may come without a buffer
   NNB_REQUIRE(nnb_aligned16(x), "sumsq_noalloc: input must be 16-byte aligned");
   NNB_REQUIRE(n >= 0 && n <= NNB_SUMSQ_NOALLOC_MAX_ELEMS, "sumsq_noalloc: n=%lld is outside [0, %lld]", n,
               (long long)NNB_SUMSQ_NOALLOC_MAX_ELEMS);

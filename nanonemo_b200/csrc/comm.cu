@@ -288,6 +288,100 @@ __global__ void __launch_bounds__(kCommThreads, 3) peer_fetch_kernel(Peers P, co
   block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // owners may rewrite once everybody has read
 }
 
+// ---- vocabulary-parallel embedding (tensor + sequence parallel): the table is sharded over the vocabulary, the residual
+// stream over the tokens. Token i (of N = world * per) belongs to rank i / per; its row lives on the rank whose vocabulary
+// slice [v0, v0 + V) holds idx[i]. Exactly one rank owns each row, so nothing is reduced: the forward PUSHES every owned row
+// into the token owner's staging buffer (peer stores), the backward PULLS the gradient rows of the tokens it owns from the
+// token owners' staging buffers (peer loads) and adds them into its slice of the table's gradient. Block b of every rank
+// handles the staging rows r with r % gridDim.x == b, so the block-to-block flag barrier orders every row it touches.
+// The staging buffer ([per, D] elements of TO, symmetric) is free again when either kernel ends (closing barrier).
+template <typename TO>
+__device__ __forceinline__ void ld_sys8(const TO* p, float (&v)[8]) {
+  if constexpr (sizeof(TO) == 4) {
+    const float4 a = ld_peer_f4(reinterpret_cast<const float*>(p)), b = ld_peer_f4(reinterpret_cast<const float*>(p) + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    uint4 raw;
+    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "l"(p) : "memory");
+    const TO* h = reinterpret_cast<const TO*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(h[i]);
+  }
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(kCommThreads, 3) vp_embed_fwd_kernel(Peers P, const long long* __restrict__ idx, const float* __restrict__ W,
+                                                                       TO* __restrict__ out, long long per, int D, long long v0, long long V,
+                                                                       int rank, int world, uint32_t* epochs, int slot_blocks,
+                                                                       unsigned long long timeout_ns, int* status) {
+  const uint32_t epoch = next_block_epoch(epochs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5, vec = D >> 3;
+  const long long mine = per > blockIdx.x ? (per - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;  // staging rows of this block
+  for (long long it = warp; it < mine * world; it += nwarps) {
+    const int dest = (int)(it / mine);
+    const long long r = blockIdx.x + (it - dest * mine) * gridDim.x;
+    const long long tok = idx[dest * per + r] - v0;
+    if (tok < 0 || tok >= V) continue;  // another rank's row
+    const float* src = W + tok * D;
+    TO* dst = static_cast<TO*>(P.data[dest]) + r * D;
+    for (int c = lane; c < vec; c += 32) {
+      float v[8];
+      Chunk8<float>::load(src + c * 8, v);
+      Chunk8<TO>::store(dst + c * 8, v);
+    }
+  }
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // every owner has written
+  if (ok) {
+    const TO* stage = static_cast<const TO*>(P.data[rank]);
+    for (long long it = warp; it < mine; it += nwarps) {
+      const long long r = blockIdx.x + it * gridDim.x;
+      for (int c = lane; c < vec; c += 32) {
+        float v[8];
+        ld_sys8(stage + r * D + c * 8, v);
+        Chunk8<TO>::store(out + r * D + c * 8, v);
+      }
+    }
+  }
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // staging may be written again
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(kCommThreads, 3) vp_embed_bwd_kernel(Peers P, const long long* __restrict__ idx, const TO* __restrict__ g,
+                                                                       float* __restrict__ dW, long long per, int D, long long v0, long long V,
+                                                                       int rank, int world, uint32_t* epochs, int slot_blocks,
+                                                                       unsigned long long timeout_ns, int* status) {
+  const uint32_t epoch = next_block_epoch(epochs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5, vec = D >> 3;
+  const long long mine = per > blockIdx.x ? (per - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  TO* stage = static_cast<TO*>(P.data[rank]);
+  for (long long it = warp; it < mine; it += nwarps) {  // this rank's gradient rows, where the peers can read them
+    const long long r = blockIdx.x + it * gridDim.x;
+    for (int c = lane; c < vec; c += 32)
+      *reinterpret_cast<uint4*>(stage + r * D + c * 8) = *reinterpret_cast<const uint4*>(g + r * D + c * 8);
+    if constexpr (sizeof(TO) == 4)
+      for (int c = lane; c < vec; c += 32)
+        *reinterpret_cast<uint4*>(stage + r * D + c * 8 + 4) = *reinterpret_cast<const uint4*>(g + r * D + c * 8 + 4);
+  }
+  const bool ok = block_barrier(P, rank, world, 0, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // every rank has staged
+  if (ok) {
+    for (long long it = warp; it < mine * world; it += nwarps) {
+      const int src_rank = (int)(it / mine);
+      const long long r = blockIdx.x + (it - src_rank * mine) * gridDim.x;
+      const long long tok = idx[src_rank * per + r] - v0;
+      if (tok < 0 || tok >= V) continue;
+      const TO* src = static_cast<const TO*>(P.data[src_rank]) + r * D;
+      float* dst = dW + tok * D;
+      for (int c = lane; c < vec; c += 32) {
+        float v[8];
+        ld_sys8(src + c * 8, v);
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 8), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 8 + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+      }
+    }
+  }
+  block_barrier(P, rank, world, 1, blockIdx.x, slot_blocks, epoch, status, 0, timeout_ns);  // staging may be written again
+}
+
 // Exercises the bounded wait: a "world" of two ranks whose flag buffers are both this GPU's buffer, so the
 // slot that the (absent) second rank would write is never written. The wait gives up after `poll_limit`
 // polls, records the status words and the kernel returns normally; the context stays usable.
@@ -424,5 +518,47 @@ extern "C" int nnb_peer_fetch(void* const* data_ptrs, void* const* flag_ptrs, co
                                                                   static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
                                                                   static_cast<int*>(status));
   NNB_LAUNCH_OK("peer_fetch");
+  return 0;
+}
+
+// Vocabulary-parallel embedding. stage_ptrs: every rank's staging buffer ([per, D] elements of the residual dtype, symmetric);
+// idx: ALL world * per token ids (int64, the same on every rank); W / dW: this rank's fp32 rows [v0, v0 + V) of the table and
+// of its gradient; out / g: this rank's `per` rows. D a multiple of 8, everything 16-byte aligned.
+static int vp_embed_checks(const char* what, const void* idx, const void* w, const void* rows, long long per, int D, long long V, int blocks,
+                           const void* epochs) {
+  NNB_REQUIRE(D > 0 && D % 8 == 0, "%s: D=%d must be a positive multiple of 8", what, D);
+  NNB_REQUIRE(per >= 0 && V > 0 && idx != nullptr && w != nullptr && rows != nullptr, "%s: bad arguments", what);
+  NNB_REQUIRE(nnb_aligned16(w) && nnb_aligned16(rows), "%s: 16-byte alignment required", what);
+  NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "%s: bad block count %d or no epoch counters", what, blocks);
+  return 0;
+}
+
+extern "C" int nnb_vp_embedding_fwd(void* const* stage_ptrs, void* const* flag_ptrs, const void* idx, const void* W, void* out, long long per,
+                                    int D, long long v0, long long V, int dtype, void* status, void* epochs, int rank, int world, int blocks,
+                                    double timeout_s, cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, stage_ptrs, flag_ptrs, world) != 0) return -1;
+  if (vp_embed_checks("vp_embedding_fwd", idx, W, out, per, D, V, blocks, epochs) != 0) return -1;
+  NNB_DISPATCH(dtype, TO, {
+    vp_embed_fwd_kernel<TO><<<blocks, kCommThreads, 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const float*>(W), static_cast<TO*>(out),
+                                                            per, D, v0, V, rank, world, static_cast<uint32_t*>(epochs), blocks,
+                                                            timeout_ns_of(timeout_s), static_cast<int*>(status));
+  });
+  NNB_LAUNCH_OK("vp_embedding_fwd");
+  return 0;
+}
+
+extern "C" int nnb_vp_embedding_bwd(void* const* stage_ptrs, void* const* flag_ptrs, const void* idx, const void* g, void* dW, long long per,
+                                    int D, long long v0, long long V, int dtype, void* status, void* epochs, int rank, int world, int blocks,
+                                    double timeout_s, cudaStream_t st) {
+  Peers P;
+  if (fill_peers(P, stage_ptrs, flag_ptrs, world) != 0) return -1;
+  if (vp_embed_checks("vp_embedding_bwd", idx, dW, g, per, D, V, blocks, epochs) != 0) return -1;
+  NNB_DISPATCH(dtype, TO, {
+    vp_embed_bwd_kernel<TO><<<blocks, kCommThreads, 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const TO*>(g), static_cast<float*>(dW),
+                                                            per, D, v0, V, rank, world, static_cast<uint32_t*>(epochs), blocks,
+                                                            timeout_ns_of(timeout_s), static_cast<int*>(status));
+  });
+  NNB_LAUNCH_OK("vp_embedding_bwd");
   return 0;
 }

@@ -65,6 +65,7 @@ struct BParams {
   const float* rope_sin;
 };
 
+template <bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -276,8 +277,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(prob[c * 32 + i], prob[c * 32 + i + 1]);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
+            pk[i >> 1] = pack2_16<F16>(prob[c * 32 + i], prob[c * 32 + i + 1]);
           }
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
@@ -309,8 +309,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int i = 0; i < 32; i += 2) {
             const float d0 = prob[c * 32 + i] * (__uint_as_float(rp[i]) * p.scale - Ds);
             const float d1 = prob[c * 32 + i + 1] * (__uint_as_float(rp[i + 1]) * p.scale - Ds);
-            __nv_bfloat162 d2 = __floats2bfloat162_rn(d0, d1);
-            dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
+            dk[i >> 1] = pack2_16<F16>(d0, d1);
           }
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
@@ -358,8 +357,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = (jj & 3) * 8 + 2 * e;
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
-          w[e] = *reinterpret_cast<uint32_t*>(&v2);
+          w[e] = pack2_16<F16>(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
         }
         *reinterpret_cast<uint4*>(dst + ((jj ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
@@ -391,7 +389,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 // delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; 8 lanes per (b, t, h) row of 64 elements,
 // 16 bytes per lane per tensor. The same pass clears the fp32 dQ accumulator (its rows are visited in the same order).
-__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+template <typename T16>
+__global__ void flash_delta_kernel(const T16* __restrict__ o, const T16* __restrict__ d_o,
                                    float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H, long long o_sb, long long o_st,
                                    long long o_sh, long long do_sb, long long do_st, long long do_sh) {
   const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -406,8 +405,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
     t = (int)(bt % T);
     b = (int)(bt / T);
     float a[8], g[8];
-    Chunk8<__nv_bfloat16>::load(o + b * o_sb + t * o_st + h * o_sh + sub * 8, a);
-    Chunk8<__nv_bfloat16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
+    Chunk8<T16>::load(o + b * o_sb + t * o_st + h * o_sh + sub * 8, a);
+    Chunk8<T16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
 #pragma unroll
     for (int i = 0; i < 8; ++i) s += a[i] * g[i];
     float4* z = reinterpret_cast<float4*>(dq_acc + w * HD + sub * 8);
@@ -422,7 +421,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
 
 // dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous); with tables, the inverse RoPE of position t is
 // applied on the way (columns j and j + 32 are partners, so one thread converts 8 + 8 elements).
-__global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int H,
+template <typename T16>
+__global__ void flash_dq_convert_kernel(const float* __restrict__ acc, T16* __restrict__ dq, long long rows, int H,
                                         int T, long long sb, long long st, long long sh, const float* __restrict__ rope_cos,
                                         const float* __restrict__ rope_sin) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;  // one thread per 8 + 8 elements
@@ -448,9 +448,9 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
       hi[i] = bb * c[i] - a * s[i];
     }
   }
-  __nv_bfloat16* dst = dq + b * sb + t * st + h * sh;
-  Chunk8<__nv_bfloat16>::store(dst + j, lo);
-  Chunk8<__nv_bfloat16>::store(dst + HD / 2 + j, hi);
+  T16* dst = dq + b * sb + t * st + h * sh;
+  Chunk8<T16>::store(dst + j, lo);
+  Chunk8<T16>::store(dst + HD / 2 + j, hi);
 }
 
 }  // namespace
@@ -458,13 +458,13 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
 int nnb_flash_bwd_t_impl(int hd, const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse, void* delta,
                           void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, const long long* qs,
                           const long long* ks, const long long* vs, const long long* os, const long long* dos, const long long* dqs,
-                          const long long* dks, const long long* dvs, float scale, void* status, cudaStream_t st);
+                          const long long* dks, const long long* dvs, float scale, int dtype, void* status, cudaStream_t st);
 
 #ifdef NNB_PROFILE
 extern "C" int nnb_flash_bwd_prof_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_flash_prof, sizeof(g_flash_prof)); }
 #endif
 
-// All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16.
+// All tensors are [B, T, heads, 64] views given by element strides (contiguous last dim), bf16 or fp16 (one dtype for all).
 // lse: fp32 [B, H, T] from the forward pass; delta: fp32 [B, H, T] scratch (written here);
 // dq_acc: fp32 [B, T, H, hd] contiguous scratch (cleared by the delta pre-pass; partial tiles are reduce-added into it).
 // rope_cos / rope_sin: null, or fp32 [T, 32] tables: dQ and dK are then returned through the inverse rotation (head_dim 64).
@@ -477,7 +477,8 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
                              long long dv_st, long long dv_sh, float scale, int dtype, const void* rope_cos, const void* rope_sin,
                              void* status, cudaStream_t st) {
   NNB_REQUIRE(hd == HD || hd == 128, "flash_bwd: head_dim %d not supported (64, 128)", hd);
-  NNB_REQUIRE(dtype == NNB_BF16, "flash_bwd: bf16 only");
+  NNB_REQUIRE(dtype == NNB_BF16 || dtype == NNB_F16, "flash_bwd: bf16 or fp16 only (dtype code %d)", dtype);
+  const bool f16 = dtype == NNB_F16;
   NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_bwd: bad shape");
   // head_dim 128 runs on the transposed-tile kernel (flash_bwd_t.cu). It also serves head_dim 64
   // (NANONEMO_FLASH_BWD=transposed), but there the 128 x 128 formulation of this file measured faster (0.43 vs 0.57 ms at
@@ -491,9 +492,9 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
     const long long dos[3] = {do_sb, do_st, do_sh}, dqs[3] = {dq_sb, dq_st, dq_sh}, dks[3] = {dk_sb, dk_st, dk_sh};
     const long long dvs[3] = {dv_sb, dv_st, dv_sh};
     return nnb_flash_bwd_t_impl(hd, q, k, v, o, d_o, lse, delta, dq_acc, dq, dk, dv, B, T, H, KVH, qs, ks, vs, os, dos, dqs, dks, dvs,
-                                scale, status, st);
+                                scale, dtype, status, st);
   }
-  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (!nnb_make_tmap_4d(&tq, dt, 2, q, hd, H, T, B, q_sh * 2, q_st * 2, q_sb * 2, 64, 1, BQ, "flash_bwd Q")) return -4;
   if (!nnb_make_tmap_4d(&tk, dt, 2, k, hd, KVH, T, B, k_sh * 2, k_st * 2, k_sb * 2, 64, 1, BKV, "flash_bwd K")) return -4;
@@ -505,8 +506,13 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   if (!nnb_make_tmap_4d(&tdv, dt, 2, dv, hd, KVH, T, B, dv_sh * 2, dv_st * 2, dv_sb * 2, 64, 1, BKV, "flash_bwd dV")) return -4;
 
   const long long rows = (long long)B * T * H;
-  flash_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
-                                                                          (float*)delta, (float*)dq_acc, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
+  const unsigned delta_blocks = (unsigned)((rows * 8 + 255) / 256);
+  if (f16)
+    flash_delta_kernel<__half><<<delta_blocks, 256, 0, st>>>((const __half*)o, (const __half*)d_o, (float*)delta, (float*)dq_acc, B, T, H, o_sb,
+                                                            o_st, o_sh, do_sb, do_st, do_sh);
+  else
+    flash_delta_kernel<__nv_bfloat16><<<delta_blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, (float*)delta,
+                                                                   (float*)dq_acc, B, T, H, o_sb, o_st, o_sh, do_sb, do_st, do_sh);
   NNB_LAUNCH_OK("flash_delta");
 
   BParams p{};
@@ -517,25 +523,33 @@ extern "C" int nnb_flash_bwd(const void* q, const void* k, const void* v, const 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = static_cast<const float*>(lse);
   p.delta = static_cast<const float*>(delta);
-  p.idesc_s = sm100::make_idesc_f16(1, 0, 0, BQ, BKV);
-  p.idesc_dkv = sm100::make_idesc_f16(1, 1, 1, BKV, HD);
-  p.idesc_dq = sm100::make_idesc_f16(1, 0, 1, BQ, HD);
+  const int fmt = f16 ? 0 : 1;
+  p.idesc_s = sm100::make_idesc_f16(fmt, 0, 0, BQ, BKV);
+  p.idesc_dkv = sm100::make_idesc_f16(fmt, 1, 1, BKV, HD);
+  p.idesc_dq = sm100::make_idesc_f16(fmt, 0, 1, BQ, HD);
   p.status = static_cast<int*>(status);
   p.rope_cos = static_cast<const float*>(rope_cos);
   p.rope_sin = static_cast<const float*>(rope_sin);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
       nnb_set_error("flash_bwd: cannot reserve %d bytes of shared memory", kSmem);
       return -3;
     }
     configured = true;
   }
   dim3 grid(KVH, B, (T + BKV - 1) / BKV);
-  flash_bwd_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
+  if (f16) flash_bwd_kernel<true><<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
+  else flash_bwd_kernel<false><<<grid, kThreads, kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   NNB_LAUNCH_OK("flash_bwd");
-  flash_dq_convert_kernel<<<(unsigned)((rows * (HD / 16) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows,
-                                                                                     H, T, dq_sb, dq_st, dq_sh, p.rope_cos, p.rope_sin);
+  const unsigned conv_blocks = (unsigned)((rows * (HD / 16) + 255) / 256);
+  if (f16)
+    flash_dq_convert_kernel<__half><<<conv_blocks, 256, 0, st>>>((const float*)dq_acc, (__half*)dq, rows, H, T, dq_sb, dq_st, dq_sh, p.rope_cos,
+                                                                p.rope_sin);
+  else
+    flash_dq_convert_kernel<__nv_bfloat16><<<conv_blocks, 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq, rows, H, T, dq_sb, dq_st, dq_sh,
+                                                                       p.rope_cos, p.rope_sin);
   NNB_LAUNCH_OK("flash_dq_convert");
   return 0;
 }

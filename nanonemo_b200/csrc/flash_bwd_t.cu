@@ -59,7 +59,7 @@ struct BParams {
   int* status;
 };
 
-template <int HD>
+template <int HD, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -276,9 +276,8 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             pv[e] = prob;
             dv[e] = prob * (__uint_as_float(rp[i + e]) * p.scale - sD[c]);
           }
-          __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]), d2 = __floats2bfloat162_rn(dv[0], dv[1]);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&a);
-          dk[i >> 1] = *reinterpret_cast<uint32_t*>(&d2);
+          pk[i >> 1] = pack2_16<F16>(pv[0], pv[1]);
+          dk[i >> 1] = pack2_16<F16>(dv[0], dv[1]);
         }
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
@@ -323,8 +322,7 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = (jj & 3) * 8 + 2 * e;
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
-            w[e] = *reinterpret_cast<uint32_t*>(&v2);
+            w[e] = pack2_16<F16>(__uint_as_float(jj < 4 ? r0[i] : r1[i]), __uint_as_float(jj < 4 ? r0[i + 1] : r1[i + 1]));
           }
           *reinterpret_cast<uint4*>(dst + ((jj ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
@@ -360,8 +358,8 @@ flash_bwd_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; HD / 8 lanes per row, 16 bytes per lane per tensor. The same pass
 // clears the fp32 dQ accumulator (its rows are visited in the same order).
-template <int HD>
-__global__ void flash_delta_t_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+template <int HD, typename T16>
+__global__ void flash_delta_t_kernel(const T16* __restrict__ o, const T16* __restrict__ d_o,
                                      float* __restrict__ delta, float* __restrict__ dq_acc, int B, int T, int H, long long o_sb, long long o_st,
                                      long long o_sh, long long do_sb, long long do_st, long long do_sh) {
   constexpr int L = HD / 8;
@@ -377,8 +375,8 @@ __global__ void flash_delta_t_kernel(const __nv_bfloat16* __restrict__ o, const 
     t = (int)(bt % T);
     b = (int)(bt / T);
     float a[8], g[8];
-    Chunk8<__nv_bfloat16>::load(o + b * o_sb + t * o_st + h * o_sh + sub * 8, a);
-    Chunk8<__nv_bfloat16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
+    Chunk8<T16>::load(o + b * o_sb + t * o_st + h * o_sh + sub * 8, a);
+    Chunk8<T16>::load(d_o + b * do_sb + t * do_st + h * do_sh + sub * 8, g);
 #pragma unroll
     for (int i = 0; i < 8; ++i) s += a[i] * g[i];
     float4* z = reinterpret_cast<float4*>(dq_acc + w * HD + sub * 8);
@@ -391,8 +389,8 @@ __global__ void flash_delta_t_kernel(const __nv_bfloat16* __restrict__ o, const 
 }
 
 // dq[b, t, h, :] (bf16, strided) = dq_acc[b, t, h, :] (fp32, contiguous)
-template <int HD>
-__global__ void flash_dq_convert_t_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int H,
+template <int HD, typename T16>
+__global__ void flash_dq_convert_t_kernel(const float* __restrict__ acc, T16* __restrict__ dq, long long rows, int H,
                                           int T, long long sb, long long st, long long sh) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;  // one thread per 8 elements
   const long long total = rows * (HD / 8);
@@ -405,16 +403,17 @@ __global__ void flash_dq_convert_t_kernel(const float* __restrict__ acc, __nv_bf
   const long long b = bt / T;
   float v[8];
   Chunk8<float>::load(acc + r * HD + j, v);
-  Chunk8<__nv_bfloat16>::store(dq + b * sb + t * st + h * sh + j, v);
+  Chunk8<T16>::store(dq + b * sb + t * st + h * sh + j, v);
 }
 
-template <int HD>
+template <int HD, bool F16>
 int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse, void* delta,
                  void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, const long long* qs, const long long* ks,
                  const long long* vs, const long long* os, const long long* dos, const long long* dqs, const long long* dks,
                  const long long* dvs, float scale, void* status, cudaStream_t st) {
   using C = Cfg<HD>;
-  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  using T16 = typename sm100::Operand16<F16>::type;
+  const CUtensorMapDataType dt = F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (!nnb_make_tmap_4d(&tq, dt, 2, q, HD, H, T, B, qs[2] * 2, qs[1] * 2, qs[0] * 2, 64, 1, BQ, "flash_bwd Q")) return -4;
   if (!nnb_make_tmap_4d(&tk, dt, 2, k, HD, KVH, T, B, ks[2] * 2, ks[1] * 2, ks[0] * 2, 64, 1, BKV, "flash_bwd K")) return -4;
@@ -426,8 +425,8 @@ int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, con
   if (!nnb_make_tmap_4d(&tdv, dt, 2, dv, HD, KVH, T, B, dvs[2] * 2, dvs[1] * 2, dvs[0] * 2, 64, 1, BKV, "flash_bwd dV")) return -4;
 
   const long long rows = (long long)B * T * H;
-  flash_delta_t_kernel<HD><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, (float*)delta, (float*)dq_acc, B, T, H, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
+  flash_delta_t_kernel<HD, T16><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>(
+      (const T16*)o, (const T16*)d_o, (float*)delta, (float*)dq_acc, B, T, H, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
   NNB_LAUNCH_OK("flash_delta");
   BParams p{};
   p.B = B; p.H = H; p.KVH = KVH; p.T = T;
@@ -437,23 +436,24 @@ int launch_bwd_t(const void* q, const void* k, const void* v, const void* o, con
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = static_cast<const float*>(lse);
   p.delta = static_cast<const float*>(delta);
-  p.idesc_s = sm100::make_idesc_f16(1, 0, 0, BKV, BQ);
-  p.idesc_dkv = sm100::make_idesc_f16(1, 0, 1, BKV, HD);
-  p.idesc_dq = sm100::make_idesc_f16(1, 1, 1, HD, BQ);
+  constexpr int fmt = F16 ? 0 : 1;
+  p.idesc_s = sm100::make_idesc_f16(fmt, 0, 0, BKV, BQ);
+  p.idesc_dkv = sm100::make_idesc_f16(fmt, 0, 1, BKV, HD);
+  p.idesc_dq = sm100::make_idesc_f16(fmt, 1, 1, HD, BQ);
   p.status = static_cast<int*>(status);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_bwd_t_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(flash_bwd_t_kernel<HD, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess) {
       nnb_set_error("flash_bwd: cannot reserve %d bytes of shared memory", C::kSmem);
       return -3;
     }
     configured = true;
   }
   dim3 grid(KVH, B, (T + BKV - 1) / BKV);
-  flash_bwd_t_kernel<HD><<<grid, kThreads, C::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
+  flash_bwd_t_kernel<HD, F16><<<grid, kThreads, C::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
   NNB_LAUNCH_OK("flash_bwd_t");
-  flash_dq_convert_t_kernel<HD><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (__nv_bfloat16*)dq,
-                                                                                           rows, H, T, dqs[0], dqs[1], dqs[2]);
+  flash_dq_convert_t_kernel<HD, T16><<<(unsigned)((rows * (HD / 8) + 255) / 256), 256, 0, st>>>((const float*)dq_acc, (T16*)dq, rows, H, T,
+                                                                                                dqs[0], dqs[1], dqs[2]);
   NNB_LAUNCH_OK("flash_dq_convert");
   return 0;
 }
@@ -469,8 +469,11 @@ extern "C" int nnb_flash_bwd_t_prof_read(unsigned long long* out) { return (int)
 int nnb_flash_bwd_t_impl(int hd, const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
                          void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int T, int H, int KVH, const long long* qs,
                          const long long* ks, const long long* vs, const long long* os, const long long* dos, const long long* dqs,
-                         const long long* dks, const long long* dvs, float scale, void* status, cudaStream_t st) {
-  if (hd == 64)
-    return launch_bwd_t<64>(q, k, v, o, d_o, lse, delta, dq_acc, dq, dk, dv, B, T, H, KVH, qs, ks, vs, os, dos, dqs, dks, dvs, scale, status, st);
-  return launch_bwd_t<128>(q, k, v, o, d_o, lse, delta, dq_acc, dq, dk, dv, B, T, H, KVH, qs, ks, vs, os, dos, dqs, dks, dvs, scale, status, st);
+                         const long long* dks, const long long* dvs, float scale, int dtype, void* status, cudaStream_t st) {
+#define NNB_BWD_T(HD_, F16_) \
+  launch_bwd_t<HD_, F16_>(q, k, v, o, d_o, lse, delta, dq_acc, dq, dk, dv, B, T, H, KVH, qs, ks, vs, os, dos, dqs, dks, dvs, scale, status, st)
+  const bool f16 = dtype == NNB_F16;
+  if (hd == 64) return f16 ? NNB_BWD_T(64, true) : NNB_BWD_T(64, false);
+  return f16 ? NNB_BWD_T(128, true) : NNB_BWD_T(128, false);
+#undef NNB_BWD_T
 }

@@ -63,7 +63,7 @@ struct FParams {
   int* status;
 };
 
-template <int HD>
+template <int HD, bool F16>
 __global__ void __launch_bounds__(kThreads, FCfg<HD>::kCtasPerSm)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FParams p) {
@@ -199,10 +199,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int HD>
+template <int HD, bool F16>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, const FParams& p,
                cudaStream_t st) {
-  auto kern = flash_fwd_kernel<HD>;
+  auto kern = flash_fwd_kernel<HD, F16>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FCfg<HD>::kSmem) != cudaSuccess) {
@@ -225,9 +225,10 @@ extern "C" int nnb_flash_fwd(const void* q, const void* k, const void* v, void* 
                              long long k_sh, long long v_sb, long long v_st, long long v_sh, long long o_sb, long long o_st,
                              long long o_sh, float scale, int dtype, void* status, cudaStream_t st) {
   NNB_REQUIRE(hd == 64 || hd == 128, "flash_fwd: head_dim %d not supported (64 or 128)", hd);
-  NNB_REQUIRE(dtype == NNB_BF16, "flash_fwd: bf16 only (dtype code %d)", dtype);
+  NNB_REQUIRE(dtype == NNB_BF16 || dtype == NNB_F16, "flash_fwd: bf16 or fp16 only (dtype code %d)", dtype);
+  const bool f16 = dtype == NNB_F16;
   NNB_REQUIRE(H % KVH == 0 && B > 0 && T > 0, "flash_fwd: bad shape B=%d T=%d H=%d KVH=%d", B, T, H, KVH);
-  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int BN = 64;
   CUtensorMap tq, tk, tv, to;
   if (!nnb_make_tmap_4d(&tq, dt, 2, q, hd, H, T, B, q_sh * 2, q_st * 2, q_sb * 2, 64, 1, BQ, "flash Q")) return -4;
@@ -240,10 +241,11 @@ extern "C" int nnb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = static_cast<float*>(lse);
-  p.idesc_qk = sm100::make_idesc_f16(1, 0, 0, BQ, BN);
-  p.idesc_pv = sm100::make_idesc_f16(1, 0, 1, BQ, hd);
+  p.idesc_qk = sm100::make_idesc_f16(f16 ? 0 : 1, 0, 0, BQ, BN);
+  p.idesc_pv = sm100::make_idesc_f16(f16 ? 0 : 1, 0, 1, BQ, hd);
   p.status = static_cast<int*>(status);
-  const int rc = hd == 64 ? launch_fwd<64>(tq, tk, tv, to, p, st) : launch_fwd<128>(tq, tk, tv, to, p, st);
+  const int rc = hd == 64 ? (f16 ? launch_fwd<64, true>(tq, tk, tv, to, p, st) : launch_fwd<64, false>(tq, tk, tv, to, p, st))
+                          : (f16 ? launch_fwd<128, true>(tq, tk, tv, to, p, st) : launch_fwd<128, false>(tq, tk, tv, to, p, st));
   if (rc != 0) return rc;
   NNB_LAUNCH_OK("flash_fwd");
   return 0;

@@ -320,6 +320,20 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int fmt_ab, int a_mn, int 
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// Two fp32 values rounded to the 16-bit operand format of the kernel (F16: IEEE half, otherwise bfloat16), packed low | high.
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2_16(float a, float b) {
+  if constexpr (F16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+template <bool F16> struct Operand16 { using type = __nv_bfloat16; };
+template <> struct Operand16<true> { using type = __half; };
+
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -19,6 +19,8 @@ import torch
 import torch.nn.functional as F
 from torch.nn.attention import SDPBackend, sdpa_kernel
 
+_ATTN_DTYPES = (torch.bfloat16, torch.float16)  # operand formats of the tensor-core attention kernels
+
 
 # ----------------------------------------------------------------------------- torch oracles
 def _wide(x: torch.Tensor) -> torch.Tensor:
@@ -163,10 +165,10 @@ def attention_packed(qkv, n_heads, n_kv_heads, head_dim, impl="torch", backend=S
     _need_cuda(qkv, "attention_packed")
     from nanonemo_b200.ops import direct, library
 
-    if direct.ENABLED and qkv.dtype == torch.bfloat16:
+    if qkv.dtype not in _ATTN_DTYPES:  # the attention kernels take 16-bit operands: fp32 inputs go through bf16 and back
+        return attention_packed(qkv.to(torch.bfloat16), n_heads, n_kv_heads, head_dim, impl, backend).to(qkv.dtype)
+    if direct.ENABLED:
         return direct.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)
-    if qkv.dtype != torch.bfloat16:  # the attention kernels are bf16: fp16 / fp32 inputs are converted and the result converted back
-        return library.flash_attn_packed(qkv.to(torch.bfloat16), n_heads, n_kv_heads, head_dim)[0].to(qkv.dtype)
     return library.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)[0]
 
 
@@ -177,8 +179,8 @@ def flash_attn(q, k, v, impl="sm100"):
     _need_cuda(q, "flash_attn")
     from nanonemo_b200.ops import library
 
-    bf = torch.bfloat16  # the attention kernels are bf16: other dtypes are converted and the result converted back
-    return library.flash_attn(q.to(bf), k.to(bf), v.to(bf))[0].to(q.dtype)
+    dt = q.dtype if q.dtype in _ATTN_DTYPES else torch.bfloat16  # 16-bit operands of one dtype; fp32 goes through bf16 and back
+    return library.flash_attn(q.to(dt), k.to(dt), v.to(dt))[0].to(q.dtype)
 
 
 def swiglu(g, u, impl="torch"):
@@ -202,10 +204,10 @@ def swiglu_packed(gu, impl="torch"):
 
 
 def fused_ok() -> bool:
-    """The block-level fused operators compute in bf16 (the attention kernels are bf16 only)."""
+    """The block-level fused operators run when the compute dtype is one the tensor-core kernels take (bf16 or fp16)."""
     from nanonemo_b200.ops.gemm import compute_dtype
 
-    return compute_dtype() == torch.bfloat16
+    return compute_dtype() in _ATTN_DTYPES
 
 
 def qkv_rope_attention(x, weight, cos, sin, n_heads, n_kv_heads, head_dim):
@@ -220,7 +222,9 @@ def qkv_rope_attention(x, weight, cos, sin, n_heads, n_kv_heads, head_dim):
 
     B, T, _ = x.shape
     c, s = _tables(cos, sin, T)
-    x2 = x.reshape(B * T, -1).to(torch.bfloat16).contiguous()
+    from nanonemo_b200.ops.gemm import compute_dtype
+
+    x2 = x.reshape(B * T, -1).to(compute_dtype()).contiguous()
     qkv = library.gemm_rope(x2, weight, c, s, T, (n_heads + n_kv_heads) * head_dim, head_dim).view(B, T, -1)
     return library.flash_attn_packed(qkv, n_heads, n_kv_heads, head_dim)[0]
 
@@ -234,7 +238,9 @@ def linear_swiglu(x, weight):
         return f(x, weight)
     from nanonemo_b200.ops import library
 
-    x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    from nanonemo_b200.ops.gemm import compute_dtype
+
+    x2 = x.reshape(-1, x.shape[-1]).to(compute_dtype()).contiguous()
     return library.gemm_swiglu(x2, weight)[1].view(*x.shape[:-1], weight.shape[0] // 2)
 
 

@@ -5,6 +5,7 @@ Raw launchers; the differentiable operators are registered in ``ops/library.py``
 (B, T, H, hd) projection are the common case) and returns (B, H, T, hd); ``flash_attn_packed(qkv, H, KVH, hd)`` reads
 the three operands straight out of the packed (B, T, (H + 2 KVH) hd) projection and writes (B, T, H hd), and its
 backward writes dQ, dK, dV into one packed gradient tensor, so no split / transpose / concat kernels run around attention.
+Operands are bf16 or fp16 (one dtype for all of them; scores, softmax and every accumulator are fp32 either way).
 Query head h reads KV head h // (H // KVH) directly (as the reference kernel does,
 nanonemo/kernels/cuda/flash_attn.cu:59,72-74). The log-sum-exp per row is saved for backward.
 """
@@ -15,6 +16,17 @@ import torch
 
 from nanonemo_b200.ops import _lib
 from nanonemo_b200.ops.gemm import status_tensor
+
+
+_CODE = {torch.bfloat16: 1, torch.float16: 2}
+
+
+def _dtype_code(*tensors):
+    """bf16 or fp16, the same for every operand (the tensor-core instruction takes one 16-bit format for A and B)."""
+    dt = tensors[0].dtype
+    if dt not in _CODE or any(t.dtype != dt for t in tensors):
+        raise TypeError(f"attention kernels take bf16 or fp16 operands of one dtype, got {[str(t.dtype) for t in tensors]}")
+    return _CODE[dt]
 
 
 def _strides_bthd(t):
@@ -31,8 +43,8 @@ def fwd_raw(q, k, v, o, scale):
     _lib.call("nnb_flash_fwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.i32(B), _lib.i32(T),
               _lib.i32(H), _lib.i32(KVH), _lib.i32(hd), *(_lib.i64(s) for s in _strides_bthd(q)),
               *(_lib.i64(s) for s in _strides_bthd(k)), *(_lib.i64(s) for s in _strides_bthd(v)),
-              *(_lib.i64(s) for s in _strides_bthd(o)), _lib.f32(scale), _lib.i32(1), _lib.ptr(status_tensor(q.device)),
-              _lib.vp(_lib.stream_ptr()))
+              *(_lib.i64(s) for s in _strides_bthd(o)), _lib.f32(scale), _lib.i32(_dtype_code(q, k, v, o)),
+              _lib.ptr(status_tensor(q.device)), _lib.vp(_lib.stream_ptr()))
     return lse
 
 
@@ -50,5 +62,6 @@ def bwd_raw(q, k, v, o, lse, do, dq, dk, dv, scale, rope_cos=None, rope_sin=None
               *(_lib.i64(s) for s in _strides_bthd(k)), *(_lib.i64(s) for s in _strides_bthd(v)),
               *(_lib.i64(s) for s in _strides_bthd(o)), *(_lib.i64(s) for s in _strides_bthd(do)),
               *(_lib.i64(s) for s in _strides_bthd(dq)), *(_lib.i64(s) for s in _strides_bthd(dk)),
-              *(_lib.i64(s) for s in _strides_bthd(dv)), _lib.f32(scale), _lib.i32(1), _lib.ptr(rope_cos), _lib.ptr(rope_sin),
+              *(_lib.i64(s) for s in _strides_bthd(dv)), _lib.f32(scale), _lib.i32(_dtype_code(q, k, v, o, do, dq, dk, dv)),
+              _lib.ptr(rope_cos), _lib.ptr(rope_sin),
               _lib.ptr(status_tensor(q.device)), _lib.vp(_lib.stream_ptr()))

@@ -155,6 +155,22 @@ class SymmetricComm:
                   _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.blocks),
                   ctypes.c_double(self.timeout_s), ctypes.c_void_p(_lib.stream_ptr()))
 
+    def vp_embedding(self, stage: "SymmetricBuffer", idx: torch.Tensor, rows: torch.Tensor, table: torch.Tensor, v0: int, backward: bool):
+        """Vocabulary-parallel embedding over this group (csrc/comm.cu: vp_embed_fwd_kernel / vp_embed_bwd_kernel). idx: all
+        world * per token ids (int64); table: this rank's fp32 rows [v0, v0 + V) of the weight (forward) or of its gradient
+        (backward, added into); rows: this rank's [per, D] output (forward) or incoming gradient (backward). `stage`: a
+        symmetric buffer of at least per * D elements of rows.dtype, free between calls."""
+        from nanonemo_b200.ops import _lib
+
+        per, D = rows.shape
+        assert idx.numel() == per * self.world and idx.dtype == torch.int64 and table.dtype == torch.float32
+        assert stage.tensor.numel() * stage.tensor.element_size() >= per * D * rows.element_size()
+        _lib.call("nnb_vp_embedding_bwd" if backward else "nnb_vp_embedding_fwd", stage.ptr_array, self.flags.ptr_array, _lib.ptr(idx),
+                  _lib.ptr(rows if backward else table), _lib.ptr(table if backward else rows), _lib.i64(per), _lib.i32(D), _lib.i64(v0),
+                  _lib.i64(table.shape[0]), _lib.i32({torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[rows.dtype]),
+                  _lib.ptr(self.status), _lib.ptr(self.epochs), _lib.i32(self.rank), _lib.i32(self.world), _lib.i32(self.blocks),
+                  ctypes.c_double(self.timeout_s), ctypes.c_void_p(_lib.stream_ptr()))
+
     def check_status(self):
         st = self.status.tolist()
         if st[0] != 0:

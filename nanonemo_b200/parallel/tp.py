@@ -20,7 +20,8 @@ slices, attend over the first half (rank 0 of the pair) or the whole (rank 1) of
 half of the query rows, contributing zeros for the other half to the reduce-scatter; their weight gradients are summed inside
 the pair. With ``comm="fused"`` (and the sm100 GEMM) the four block linears run as single kernels that do the
 collective themselves (parallel/tp_fused.py: all-gather -> GEMM and GEMM -> reduce-scatter over peer
-memory); the embedding / head / loss collectives and the CPU path use torch.distributed.
+memory) and the embedding is one kernel that stores every owned row into its token owner's memory (csrc/comm.cu:
+vp_embed_fwd_kernel / vp_embed_bwd_kernel); the head / loss collectives and the CPU path use torch.distributed.
 """
 
 import torch
@@ -110,6 +111,16 @@ class _VocabParallelEmbedding(torch.autograd.Function):
     @staticmethod
     def forward(ctx, idx_flat, weight, tp, v0, out_dtype):
         V = weight.shape[0]
+        ft = tp.fused_tp
+        ctx.in_kernel = (ft is not None and weight.dtype == torch.float32 and weight.shape[1] % 8 == 0
+                         and idx_flat.numel() // tp.world * weight.shape[1] <= ft.embed_stage.tensor.numel())
+        if ctx.in_kernel:
+            # one kernel: every rank stores the rows it owns straight into the token owners' memory (parallel/tp_fused.py)
+            idx64 = idx_flat if idx_flat.dtype == torch.int64 else idx_flat.long()
+            idx64 = idx64.contiguous()
+            ctx.save_for_backward(idx64, weight)
+            ctx.tp, ctx.v0 = tp, v0
+            return ft.embed_rows(idx64, weight.detach().contiguous(), v0, out_dtype)
         local = idx_flat - v0
         mine = (local >= 0) & (local < V)
         rows = F.embedding(local.clamp(0, V - 1), weight).to(out_dtype)
@@ -120,6 +131,17 @@ class _VocabParallelEmbedding(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
+        if ctx.in_kernel:
+            idx64, weight = ctx.saved_tensors
+            main = getattr(weight, "_main_grad", None)
+            target = main if main is not None and main.dtype == torch.float32 else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+            ctx.tp.fused_tp.embed_grad(idx64, g.contiguous(), target, ctx.v0)
+            if target is main:
+                cb = getattr(weight, "_grad_ready_cb", None)
+                if cb is not None:
+                    cb(weight, True)
+                return None, None, None, None, None
+            return None, target.to(weight.dtype), None, None, None
         local, mine, weight = ctx.saved_tensors
         g_full = ctx.tp.all_gather(g).float() * mine.unsqueeze(-1)
         main = getattr(weight, "_main_grad", None)
@@ -249,12 +271,12 @@ class TPStrategy(LocalStrategy):
         words = super().status_words()
         ft = self.tp.fused_tp
         if ft is not None:
-            words.append(ft.fg.comm_status)
+            words += [ft.fg.comm_status, ft.comm.status]
         return words
 
     def status_owners(self) -> list:
         ft = self.tp.fused_tp
-        return [ft.fg] if ft is not None else []
+        return [ft.fg, ft.comm] if ft is not None else []
 
     def global_sumsq(self):
         total = self.store.grad_sumsq()

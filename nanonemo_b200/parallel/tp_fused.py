@@ -15,7 +15,7 @@ the reference (nanonemo/distributed/tp.py:52-64), which issue separate NCCL coll
 import torch
 
 from nanonemo_b200.ops.gemm import FusedCollectiveGemm, compute_dtype, gemm, shadow_of
-from nanonemo_b200.parallel.symm import SymmetricBuffer
+from nanonemo_b200.parallel.symm import SymmetricBuffer, SymmetricComm
 
 
 class FusedTP:
@@ -27,6 +27,9 @@ class FusedTP:
         # full-size gather source/destination (tokens x widest gathered operand) and reduce-scatter target
         self.gather_buf = SymmetricBuffer(max_tokens * max_width, dtype, device, group)
         self.shard_buf = SymmetricBuffer((max_tokens // world) * max_width, dtype, device, group)
+        # vocabulary-parallel embedding: a light-kernel communicator and a staging area for this rank's rows (fp32 at most)
+        self.comm = SymmetricComm(device, group, rank, world)
+        self.embed_stage = SymmetricBuffer((max_tokens // world) * max_width, torch.float32, device, group)
 
     def gathered_matmul(self, x_shard, w, b_mn=False):
         """all-gather(x_shard over token rows) @ w^T in one kernel. Returns (y [M, N], x_full view).
@@ -41,6 +44,18 @@ class FusedTP:
     def matmul_scattered(self, a, w, b_mn=False):
         """reduce-scatter(a @ w^T over token rows) in one kernel -> this rank's [M / world, N] rows."""
         return self.fg.gemm_rs(a, w, self.shard_buf, b_mn=b_mn).clone()
+
+
+    def embed_rows(self, idx_flat, weight, v0: int, out_dtype):
+        """This rank's token rows of the vocabulary-sharded table: every rank pushes the rows it owns to the token owners."""
+        per = idx_flat.numel() // self.world
+        out = torch.empty((per, weight.shape[1]), dtype=out_dtype, device=weight.device)
+        self.comm.vp_embedding(self.embed_stage, idx_flat, out, weight, v0, backward=False)
+        return out
+
+    def embed_grad(self, idx_flat, g, table_grad, v0: int):
+        """table_grad[idx - v0] += gradient rows of the tokens whose id falls in this rank's slice, pulled from their owners."""
+        self.comm.vp_embedding(self.embed_stage, idx_flat, g, table_grad, v0, backward=True)
 
 
 class _ColumnParallel(torch.autograd.Function):

@@ -77,6 +77,35 @@ def check_collectives(d):
         ok &= rs_ok and ag_ok
         say(f"  reduce_scatter n={n}: exact={rs_ok}   all_gather: exact={ag_ok}")
         del ar, comm, buf, shards
+    return ok and check_vocab_parallel_embedding(d)
+
+
+def check_vocab_parallel_embedding(d):
+    """Forward rows and table gradient of the vocabulary-parallel embedding kernels against index arithmetic on the full table
+    (integer-valued data: the scatter-add is exact in any order). Run twice per dtype: the staging buffer is reused."""
+    rank, world, dev = d.rank, d.world, torch.device(d.device)
+    V, D, per = 64, 72, 300  # rows per rank, width (multiple of 8), tokens per rank (not a multiple of the block count)
+    comm = SymmetricComm(dev, None, rank, world)
+    stage = SymmetricBuffer(per * D, torch.float32, dev)
+    gen = torch.Generator().manual_seed(5)
+    table = torch.randint(-8, 9, (V * world, D), generator=gen).float().to(dev)
+    ok = True
+    for dtype in (torch.float32, torch.bfloat16):
+        for rep in range(2):
+            idx = torch.randint(0, V * world, (per * world,), generator=gen).to(dev)
+            grads = torch.randint(-4, 5, (per * world, D), generator=gen).to(dev).to(dtype)
+            out = torch.empty((per, D), dtype=dtype, device=dev)
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.vp_embedding(stage, idx, out, table[rank * V:(rank + 1) * V].contiguous(), rank * V, backward=False)
+            dW = torch.ones((V, D), device=dev)
+            comm.vp_embedding(stage, idx, grads[rank * per:(rank + 1) * per].contiguous(), dW, rank * V, backward=True)
+            comm.check_status()
+            want = table[idx[rank * per:(rank + 1) * per]].to(dtype)
+            want_dW = torch.ones((V * world, D), device=dev).index_add_(0, idx, grads.float())[rank * V:(rank + 1) * V]
+            good = torch.equal(out, want) and torch.equal(dW, want_dW)
+            ok &= good
+            say(f"  vocab-parallel embedding {str(dtype)[6:]} rep={rep}: exact={good}")
     return ok
 
 

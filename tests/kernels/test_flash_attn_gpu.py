@@ -85,3 +85,38 @@ def test_backward_matches_reference(B, H, KVH, T, hd):
     for got, want, name in ((q.grad, qr.grad, "dq"), (k.grad, kr.grad, "dk"), (v.grad, vr.grad, "dv")):
         err = (got.float() - want).abs().max().item()
         assert err <= 3e-2 * want.abs().max().item() + 2e-2, f"{name}: max err {err}"
+
+
+@pytest.mark.parametrize("B,H,KVH,T,hd", [(2, 4, 2, 256, 64), (1, 3, 1, 200, 64), (1, 4, 1, 384, 128), (1, 2, 2, 37, 128)])
+def test_fp16_operands_run_natively(B, H, KVH, T, hd):
+    """fp16 q / k / v go to the tensor cores as fp16 (no bf16 detour): forward and the three gradients against the fp32
+    reference, with the tighter tolerance the 10-bit mantissa allows."""
+    from nanonemo_b200 import ops
+    from nanonemo_b200.ops.gemm import check_status
+
+    torch.manual_seed(3)
+    q = torch.randn(B, H, T, hd, device=DEV).half().requires_grad_()
+    k = torch.randn(B, KVH, T, hd, device=DEV).half().requires_grad_()
+    v = torch.randn(B, KVH, T, hd, device=DEV).half().requires_grad_()
+    out = ops.flash_attn(q, k, v)
+    assert out.dtype == torch.float16
+    g = torch.randn(B, H, T, hd, device=DEV).half()
+    out.backward(g)
+    check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _ref(qr, kr, vr)
+    ref.backward(g.float())
+    torch.testing.assert_close(out.float(), ref, rtol=4e-3, atol=4e-3)
+    for got, want, name in ((q.grad, qr.grad, "dq"), (k.grad, kr.grad, "dk"), (v.grad, vr.grad, "dv")):
+        assert got.dtype == torch.float16
+        err = (got.float() - want).abs().max().item()
+        assert err <= 6e-3 * want.abs().max().item() + 4e-3, f"{name}: max err {err}"
+
+
+def test_mixed_operand_dtypes_are_refused():
+    from nanonemo_b200.ops import attention
+
+    q = torch.randn(1, 128, 1, 64, device=DEV).half()
+    k = torch.randn(1, 128, 1, 64, device=DEV).bfloat16()
+    with pytest.raises(TypeError):
+        attention.fwd_raw(q, k, k, torch.empty_like(q), 0.125)

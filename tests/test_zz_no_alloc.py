@@ -33,11 +33,13 @@ def test_noalloc_sumsq_matches_regular_entry_point_twice(n):
         x = torch.randn(n, device="cuda") * (call + 1)
         want = sumsq(x)
         got = torch.full((), -1.0, device="cuda")
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
         rc = _noalloc(lib, x, got)
         assert rc == 0, lib.nnb_last_error()
-        assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        # neither PyTorch's caching allocator nor the driver (cudaMemGetInfo sees every cudaMalloc of the process) gave anything out
+        assert torch.cuda.memory_allocated() == before and torch.cuda.mem_get_info()[0] >= free_before
         torch.testing.assert_close(got, want, rtol=1e-5, atol=0)
         torch.testing.assert_close(got, x.double().pow(2).sum().float(), rtol=1e-5, atol=0)
 
@@ -55,3 +57,7 @@ def test_noalloc_rejects_oversized_and_null():
     assert fn(x.data_ptr(), (1 << 32) + 1, out.data_ptr(), 0) < 0
     assert b"outside" in lib.nnb_last_error()
     assert fn(None, 16, out.data_ptr(), 0) < 0
+    out.fill_(7.0)
+    assert fn(None, 0, out.data_ptr(), 0) == 0  # an empty input needs no buffer: the sum is zero
+    torch.cuda.synchronize()
+    assert out.item() == 0.0

@@ -25,6 +25,9 @@ def test_tables_from_results_only(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     text = (out / "tables.md").read_text()
     assert "| b200 | s0_fp32 | 1,000 | 16.00 |" in text and "| b200-x2 | ddp | 5,000 | 2 |" in text and "| qkv | 0.1 |" in text
+    # figures are plain SVG files: one bar per ladder stage, one per multi-GPU row
+    bars = (out / "ladder_tokens_per_s.svg").read_text()
+    assert bars.startswith("<svg") and bars.count("<rect") == 1 + 2 and "s1_fp16" in bars and (out / "dist_tokens_per_s.svg").exists()
     # the README block between the markers is regenerated from the same tables, text around it is kept
     readme = tmp_path / "README.md"
     readme.write_text("intro\n<!-- results:begin -->\nstale number 123\n<!-- results:end -->\noutro\n")
@@ -33,6 +36,24 @@ def test_tables_from_results_only(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     new = readme.read_text()
     assert new.startswith("intro\n") and new.endswith("outro\n") and "stale number" not in new and "| b200 | s1_fp16 | 2,000 | 8.00 |" in new
+
+
+def test_loss_curve_and_tick_values(tmp_path):
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("make_figures", ROOT / "scripts" / "make_figures.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.nice_ticks(0.0, 950_000.0) == [0.0, 200000.0, 400000.0, 600000.0, 800000.0, 1000000.0]
+    assert mod.nice_ticks(3.2, 10.9)[0] <= 3.2 and mod.nice_ticks(3.2, 10.9)[-1] >= 10.9
+    assert mod.human(1_500_000.0) == "1.5M" and mod.human(12.0) == "12"
+    metrics = tmp_path / "metrics.jsonl"
+    recs = [{"step": i, "tokens": (i + 1) * 1000, "loss": 10.0 - 0.1 * i} for i in range(20)] + [{"step": 9, "val_loss": 9.3}]
+    metrics.write_text("\n".join(json.dumps(r) for r in recs) + "\n")
+    (tmp_path / "results").mkdir()
+    mod.main(["--results", str(tmp_path / "results"), "--out", str(tmp_path / "fig"), "--metrics", str(metrics)])
+    svg = (tmp_path / "fig" / "loss.svg").read_text()
+    assert svg.count("<path") == 2 and ">train<" in svg and ">val<" in svg
 
 
 def test_nvtx_spans_are_noops_without_cuda(monkeypatch):
