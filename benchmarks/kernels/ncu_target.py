@@ -2,7 +2,7 @@
 a few hundred MB, so an `ncu --set full` capture ends by itself in about a minute.
 
     python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,gemm_swiglu,gemm_rope,flash,flash128,rmsnorm,swiglu,rope,
-                                             ce,adamw,embedding,quantize} [iters]
+                                             ce,adamw,embedding,quantize}[,more targets] [iters]
 """
 
 import sys
@@ -15,9 +15,8 @@ import torch  # noqa: E402
 from nanonemo_b200 import ops  # noqa: E402
 
 
-def main():
-    kind = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+def build(kind: str):
+    """-> a callable that launches the kernels of target `kind` once (inputs are created here, outside the captured launches)."""
     dev, bf = "cuda", torch.bfloat16
     M = 32768
     if kind == "gemm":
@@ -94,10 +93,20 @@ def main():
                                 grad_norm_sq=sumsq(g), max_norm=1.0)
     else:
         raise SystemExit(f"unknown target {kind}")
-    for _ in range(iters):
-        fn()
-    torch.cuda.synchronize()
-    print("done", kind)
+    return fn
+
+
+def main():
+    kinds = (sys.argv[1] if len(sys.argv) > 1 else "gemm").split(",")  # several targets: one after the other, inputs freed in between
+    iters = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+    for kind in kinds:
+        fn = build(kind)
+        for _ in range(iters):
+            fn()
+        torch.cuda.synchronize()
+        del fn
+        torch.cuda.empty_cache()
+        print("done", kind, flush=True)
 
 
 if __name__ == "__main__":

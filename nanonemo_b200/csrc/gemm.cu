@@ -764,6 +764,18 @@ extern "C" int nnb_gemm_rope(const void* X, const void* W, void* QKV, const void
   return nnb_gemm2_launch(g, st);
 }
 
+// dgu[M, 2F] = SwiGLU backward of (dy[M, K] @ w_down[K, F]) against the saved projection gu[M, 2F]: the gradient of the
+// activation is formed in tensor memory and leaves as d(gate) | d(up), never as a tensor of its own. w_down is the
+// row-parallel weight as stored ([K = d_model, F], i.e. MN-major for this product).
+extern "C" int nnb_gemm_swiglu_bwd(const void* dY, const void* Wdown, const void* GU, void* dGU, int M, int F, int K, long long lda,
+                                   long long ldw, long long ldgu, long long lddgu, int dtype, void* status, cudaStream_t st) {
+  NnbGemm2Args g{};
+  if (int rc = fused_gemm_common(g, dY, Wdown, dGU, M, F, K, lda, ldw, lddgu, dtype, status)) return rc;
+  g.b_mn = 1;
+  g.epilogue = EPI_SWIGLU_BWD; g.E = const_cast<void*>(GU); g.lde = ldgu;
+  return nnb_gemm2_launch(g, st);
+}
+
 // logits[M, N] = x[M, K] @ w[N, K]^T (16-bit) plus stats[M, ceil(N / 256), 2] = (max, sum of exp(x - max)) of every
 // 256-column tile of every row, computed on the stored (rounded) logits. N must be a multiple of 64.
 extern "C" int nnb_gemm_ce_stats(const void* X, const void* W, void* logits, void* stats, int M, int N, int K, long long lda,

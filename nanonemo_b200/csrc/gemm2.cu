@@ -37,15 +37,20 @@ using namespace sm100;
 constexpr int BM = 128;   // rows per CTA (256 per pair)
 constexpr int BN = 256;   // columns per pair tile; each CTA stages BN / 2 rows of B
 constexpr int BK = 64;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueThreads = 128;  // one epilogue GROUP: four warps, one per tensor-memory lane quadrant
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = (BN / 2) * BK * 2, kStageBytes = kStageBytesA + kStageBytesB;
 constexpr int kTmemCols = 512;
-// The SwiGLU epilogue fills three staging tiles at once (gate, up, act): one stage less for the operand ring.
+// The SwiGLU epilogue fills three staging tiles at once (gate, up, act), its backward keeps two (gate, up) tile pairs in
+// flight (one being computed on / stored, one being loaded): one stage less for the operand ring.
 template <int EPI> struct Cfg {
-  static constexpr int kStages = EPI == EPI_SWIGLU ? 5 : 6;
-  static constexpr int kStagingTiles = EPI == EPI_SWIGLU ? 3 : 2;
+  static constexpr int kStages = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) ? 5 : 6;
+  static constexpr int kStagingTiles = EPI == EPI_SWIGLU ? 3 : (EPI == EPI_SWIGLU_BWD ? 4 : 2);
   static constexpr int kStagingBytes = kStagingTiles * BM * 128;
+  // Epilogue groups of four warps. The SwiGLU backward does the most arithmetic per accumulator element (a sigmoid and both
+  // products, operands read from shared memory): two groups take alternate 64-column chunks, each with its own staging
+  // pair, barrier and elected thread, so one group's stores and loads overlap the other's arithmetic.
+  static constexpr int kEpiGroups = EPI == EPI_SWIGLU_BWD ? 2 : 1;
+  static constexpr int kThreads = 64 + kEpiGroups * kEpilogueThreads;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
@@ -147,7 +152,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
 }
 
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<EPI>::kThreads, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmE, const Params2 p) {
   constexpr int kStages = Cfg<EPI>::kStages, kStagingBytes = Cfg<EPI>::kStagingBytes;
@@ -158,9 +163,10 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_tfull = bar_empty + 8 * kStages, bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  const uint32_t bar_in = bar_tempty + 16;  // EPI_SWIGLU_BWD: the (gate, up) tiles of staging pair 0 / 1 have landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_abort = abort_flag + 1;
+  volatile int* epi_abort_base = abort_flag + 1;  // one word per epilogue group
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -171,10 +177,12 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 2 * (kEpilogueThreads / 32));  // leader: epilogue warps of both CTAs
+      mbar_init(bar_tempty + 8 * a, 2 * Cfg<EPI>::kEpiGroups * (kEpilogueThreads / 32));  // leader: epilogue warps of both CTAs
+      mbar_init(bar_in + 8 * a, 1);
     }
     *abort_flag = 0;
-    *epi_abort = 0;
+    epi_abort_base[0] = 0;
+    epi_abort_base[1] = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -186,7 +194,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmD);
-    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmE);
+    if (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) tma_prefetch_desc(&tmE);
   }
   tc_fence_before();
   __syncthreads();
@@ -277,8 +285,12 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    const int et = threadIdx.x - 64;
+    const int grp = Cfg<EPI>::kEpiGroups == 1 ? 0 : (threadIdx.x - 64) / kEpilogueThreads;  // epilogue group
+    const int et = (threadIdx.x - 64) % kEpilogueThreads;           // thread within the group; et == 0 issues its TMA traffic
+    const int epi_bar = 1 + grp;                                    // the group's named barrier
+    volatile int* epi_abort = epi_abort_base + grp;
     uint32_t tile_iter = 0, gchunk = 0;
+    uint32_t in_count = 0;  // EPI_SWIGLU_BWD: loads this group has consumed from its staging pair (parity of the next wait)
     int pending_stores = 0;
     const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
     for (int item = pair0; item < items; item += npairs, ++tile_iter) {
@@ -295,11 +307,48 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           load_table32(p.sin_t + (size_t)t * 32, rope_s);
         }
       }
+      // EPI_SWIGLU_BWD: the saved (gate, up) values of this tile arrive by TMA in 64-column chunks; group g takes chunks g,
+      // g + 2 into staging pair g. Its first chunk is requested here, while the tile is still being multiplied.
+      int bwd_chunks = 0;
+      auto load_gu_chunk = [&](int c) {  // the group's thread et == 0 only; its staging pair must not be the source of a store in flight
+        const uint32_t bar = bar_in + 8 * grp, dst = smem_u32(staging + grp * 2 * (BM * 128));
+        mbar_expect_tx(bar, 2 * BM * 128);
+        tma_load_2d(dst, &tmE, bar, n_blk * BN + c * 64, d_row);
+        tma_load_2d(dst + BM * 128, &tmE, bar, p.N + n_blk * BN + c * 64, d_row);
+      };
+      if constexpr (EPI == EPI_SWIGLU_BWD) {
+        if (d_row < p.M) bwd_chunks = min(BN / 64, (p.N - n_blk * BN) / 64);
+        if (et == 0) {
+          if (grp < bwd_chunks) {
+            if (pending_stores > 0) tma_wait_group_read<0>();
+            load_gu_chunk(grp);
+          }
+          // The group's loads form a chain (a pair is reloaded only after its stores have drained), so their latency is
+          // exposed: pull this tile's later chunk and the NEXT tile's chunks into L2 now, a whole tile ahead of their use.
+          auto prefetch_gu = [&](int nb, int r0, int c) {
+            tma_prefetch_l2_2d(&tmE, nb * BN + c * 64, r0);
+            tma_prefetch_l2_2d(&tmE, p.N + nb * BN + c * 64, r0);
+          };
+          if (grp + 2 < bwd_chunks) prefetch_gu(n_blk, d_row, grp + 2);
+          if (item + npairs < items) {
+            int m2, n2;
+            tile_coords((item + npairs) / p.k_splits, m2, n2);
+            const int r2 = (m2 * 2 + (int)rank) * BM;
+            const int ch2 = r2 < p.M ? min(BN / 64, (p.N - n2 * BN) / 64) : 0;
+            for (int c = grp; c < ch2; c += 2) prefetch_gu(n2, r2, c);
+          }
+        }
+      }
       const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag);
       if (!ok) { fail_role = 3; fail_item = item; }
       if (et == 0) *epi_abort = *abort_flag;
-      named_barrier_sync(1, kEpilogueThreads);
-      if (*epi_abort) break;
+      named_barrier_sync(epi_bar, kEpilogueThreads);
+      if (*epi_abort) {
+        if constexpr (EPI == EPI_SWIGLU_BWD) {  // the tile loads requested above must have landed before shared memory is given up
+          if (grp < bwd_chunks) mbar_wait(bar_in + 8 * grp, (in_count++) & 1, abort_flag);
+        }
+        break;
+      }
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       const bool rows_live = d_row < p.M;  // an odd number of 128-row blocks leaves the peer's last block outside the matrix
@@ -313,7 +362,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const int fcol = n_blk * (BN / 2) + c * 64;
           if (fcol >= F) break;
           if (et == 0 && pending_stores > 0) tma_wait_group_read<0>();
-          named_barrier_sync(1, kEpilogueThreads);
+          named_barrier_sync(epi_bar, kEpilogueThreads);
           uint8_t* row_g = staging + row * 128;
           uint8_t* row_u = row_g + BM * 128;
           uint8_t* row_a = row_u + BM * 128;
@@ -335,12 +384,59 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             stage32(row_a, sw, h * 4, wa);
           }
           fence_proxy_async_smem();
-          named_barrier_sync(1, kEpilogueThreads);
+          named_barrier_sync(epi_bar, kEpilogueThreads);
           if (et == 0) {
             tma_store_2d(&tmD, smem_u32(staging), fcol, d_row);
             tma_store_2d(&tmD, smem_u32(staging + BM * 128), F + fcol, d_row);
             tma_store_2d(&tmE, smem_u32(staging + 2 * BM * 128), fcol, d_row);
             tma_commit_group();
+          }
+          pending_stores = 1;
+        }
+      } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+        // accumulator = d(act); the group's staging pair holds gate | up of the chunk's 64 features for this CTA's 128 rows
+        // (same swizzled layout the stores use). Each thread turns its own row's slots into d(gate) | d(up) in place:
+        //   s = sigmoid(g), d(gate) = d(act) u s (1 + g (1 - s)), d(up) = d(act) g s
+        // then the two tiles are stored at columns col and F + col of the projection's gradient.
+        for (int c = grp; c < bwd_chunks; c += 2) {
+          uint8_t* g_tile = staging + grp * 2 * (BM * 128);
+          if (!mbar_wait(bar_in + 8 * grp, (in_count++) & 1, abort_flag)) { fail_role = 3; fail_item = item; }
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_row + c * 64, r0);
+          tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          uint8_t* row_g = g_tile + row * 128;
+          uint8_t* row_u = row_g + BM * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4* pg = reinterpret_cast<uint4*>(row_g + ((j ^ sw) << 4));
+            uint4* pu = reinterpret_cast<uint4*>(row_u + ((j ^ sw) << 4));
+            const uint4 gw = *pg, uw = *pu;
+            const uint32_t gin[4] = {gw.x, gw.y, gw.z, gw.w}, uin[4] = {uw.x, uw.y, uw.z, uw.w};
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = (j & 3) * 8 + 2 * e;
+              const float d0 = __uint_as_float(j < 4 ? r0[i] : r1[i]), d1 = __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]);
+              const float2 g2 = unpack16(gin[e], bf), u2 = unpack16(uin[e], bf);
+              const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+              og[e] = pack16(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)), bf);
+              ou[e] = pack16(d0 * g2.x * s0, d1 * g2.y * s1, bf);
+            }
+            *pg = make_uint4(og[0], og[1], og[2], og[3]);
+            *pu = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(epi_bar, kEpilogueThreads);
+          if (et == 0) {
+            const int col = n_blk * BN + c * 64;
+            tma_store_2d(&tmD, smem_u32(g_tile), col, d_row);
+            tma_store_2d(&tmD, smem_u32(g_tile + BM * 128), p.N + col, d_row);
+            tma_commit_group();
+            if (c + 2 < bwd_chunks) {
+              tma_wait_group_read<0>();  // the stores just issued have left this pair: it can take the chunk after next
+              load_gu_chunk(c + 2);
+            }
           }
           pending_stores = 1;
         }
@@ -353,7 +449,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
             ++gchunk;
             if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
-            named_barrier_sync(1, kEpilogueThreads);
+            named_barrier_sync(epi_bar, kEpilogueThreads);
             uint32_t r0[32], r1[32], w0[16], w1[16];
             tmem_ld_32x32b_x32(t_row + c * 64, r0);
             tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
@@ -364,7 +460,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             stage32(buf + row * 128, sw, 0, w0);
             stage32(buf + row * 128, sw, 4, w1);
             fence_proxy_async_smem();
-            named_barrier_sync(1, kEpilogueThreads);
+            named_barrier_sync(epi_bar, kEpilogueThreads);
             if (et == 0) {
               tma_store_2d(&tmD, smem_u32(buf), gcol, d_row);
               tma_commit_group();
@@ -379,7 +475,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const int gcol = n_blk * BN + g * 128;
             if (gcol >= p.N) break;
             if (et == 0 && pending_stores > 0) tma_wait_group_read<0>();
-            named_barrier_sync(1, kEpilogueThreads);
+            named_barrier_sync(epi_bar, kEpilogueThreads);
             uint8_t* row_lo = staging + row * 128;
             uint8_t* row_hi = row_lo + BM * 128;
 #pragma unroll
@@ -400,7 +496,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               stage32(row_hi, sw, h * 4, w1);
             }
             fence_proxy_async_smem();
-            named_barrier_sync(1, kEpilogueThreads);
+            named_barrier_sync(epi_bar, kEpilogueThreads);
             if (et == 0) {
               tma_store_2d(&tmD, smem_u32(staging), gcol, d_row);
               tma_store_2d(&tmD, smem_u32(staging + BM * 128), gcol + 64, d_row);
@@ -419,7 +515,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
           ++gchunk;
           if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
-          named_barrier_sync(1, kEpilogueThreads);
+          named_barrier_sync(epi_bar, kEpilogueThreads);
           uint8_t* my_row = buf + row * 128;
           if (p.out_f32) {
             uint32_t r[32];
@@ -457,7 +553,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             stage32(my_row, sw, 4, w1);
           }
           fence_proxy_async_smem();
-          named_barrier_sync(1, kEpilogueThreads);
+          named_barrier_sync(epi_bar, kEpilogueThreads);
           if (et == 0) {
             if (p.reduce_add) tma_reduce_add_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
             else tma_store_2d(&tmD, smem_u32(buf), n_blk * BN + col0, d_row);
@@ -515,7 +611,7 @@ int max_resident_pairs() {
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * (nnb_num_sms() / 2));
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(Cfg<EPI>::kThreads);
     cfg.dynamicSmemBytes = Cfg<EPI>::kSmemBytes;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -557,6 +653,10 @@ int launch2(const NnbGemm2Args& a, cudaStream_t st) {
   } else if (EPI == EPI_CE_STATS) {
     NNB_REQUIRE(!a.out_f32 && !a.accumulate && a.N % 64 == 0 && a.stats != nullptr, "gemm_ce_stats: 16-bit output with N a multiple of 64 expected");
     p.stats = static_cast<float*>(a.stats);
+  } else if (EPI == EPI_SWIGLU_BWD) {
+    NNB_REQUIRE(!a.out_f32 && !a.accumulate && a.N % 64 == 0 && a.E != nullptr && nnb_aligned16(a.E) && a.lde % 8 == 0,
+                "gemm_swiglu_bwd: 16-bit output, F a multiple of 64 and an aligned saved projection expected");
+    p.epi_cols = a.N;
   }
   int splits = 1;
   if (a.out_f32) {
@@ -595,8 +695,11 @@ int launch2(const NnbGemm2Args& a, cudaStream_t st) {
   else         { if (!nnb_make_tmap_2d(&tmB, in_dt, 2, a.B, a.K, a.N, a.ldb * 2, BK, 64, "gemm2 B^T")) return -4; }
   const CUtensorMapDataType d_dt = a.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : in_dt;
   const int d_bytes = a.out_f32 ? 4 : 2, d_box = a.out_f32 ? 32 : 64;
-  if (!nnb_make_tmap_2d(&tmD, d_dt, d_bytes, a.D, a.M, a.N, a.ldd * d_bytes, BM, d_box, "gemm2 D")) return -4;
+  // (EPI_SWIGLU_BWD writes d(gate) | d(up): its output, like the projection it reads through tmE, is 2 N columns wide)
+  const int d_cols = EPI == EPI_SWIGLU_BWD ? 2 * a.N : a.N;
+  if (!nnb_make_tmap_2d(&tmD, d_dt, d_bytes, a.D, a.M, d_cols, a.ldd * d_bytes, BM, d_box, "gemm2 D")) return -4;
   tmE = tmD;
+  if (EPI == EPI_SWIGLU_BWD && !nnb_make_tmap_2d(&tmE, in_dt, 2, a.E, a.M, 2 * a.N, a.lde * 2, BM, 64, "gemm2 gate|up")) return -4;
   if (EPI == EPI_SWIGLU && !nnb_make_tmap_2d(&tmE, in_dt, 2, a.E, a.M, a.N / 2, a.lde * 2, BM, 64, "gemm2 act")) return -4;
   if (a.out_f32 && !a.accumulate && p.k_splits > 1) {
     if (a.ldd == a.N) cudaMemsetAsync(a.D, 0, (size_t)a.M * a.N * 4, st);
@@ -604,7 +707,7 @@ int launch2(const NnbGemm2Args& a, cudaStream_t st) {
   }
   const int items = p.m_pairs * p.n_blocks * p.k_splits;
   const int grid = 2 * min(items, pairs);
-  gemm2_tcgen05_kernel<EPI><<<grid, kThreads, Cfg<EPI>::kSmemBytes, st>>>(tmA, tmB, tmD, tmE, p);
+  gemm2_tcgen05_kernel<EPI><<<grid, Cfg<EPI>::kThreads, Cfg<EPI>::kSmemBytes, st>>>(tmA, tmB, tmD, tmE, p);
   NNB_LAUNCH_OK("gemm2_tcgen05");
   return 0;
 }
@@ -617,6 +720,7 @@ int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
     case EPI_SWIGLU: return launch2<EPI_SWIGLU>(a, st);
     case EPI_ROPE: return launch2<EPI_ROPE>(a, st);
     case EPI_CE_STATS: return launch2<EPI_CE_STATS>(a, st);
+    case EPI_SWIGLU_BWD: return launch2<EPI_SWIGLU_BWD>(a, st);
     default: nnb_set_error("gemm2: unknown epilogue %d", a.epilogue); return -1;
   }
 }

@@ -3,7 +3,7 @@
 #include <cuda_runtime.h>
 
 // Work fused into the epilogue while a tile leaves tensor memory (see gemm2.cu).
-enum NnbGemm2Epilogue : int { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE = 2, EPI_CE_STATS = 3 };
+enum NnbGemm2Epilogue : int { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE = 2, EPI_CE_STATS = 3, EPI_SWIGLU_BWD = 4 };
 
 struct NnbGemm2Args {
   const void *A, *B;
@@ -22,6 +22,8 @@ struct NnbGemm2Args {
   // fp32 tables [t_len, head_dim / 2]
   const void *cos_t = nullptr, *sin_t = nullptr;
   int t_len = 0, rope_cols = 0, head_dim = 0;
+  // EPI_SWIGLU_BWD: the product [M, N = F] is the gradient of act = silu(gate) * up; E = the saved projection gate||up
+  // [M, 2 F] (row stride lde), D = its gradient [M, 2 F] (row stride ldd); the product itself is never stored
   // EPI_CE_STATS: fp32 [M, ceil(N / 256), 2] receiving (max, sum of exp(x - max)) of every 256-column tile of every row
   void* stats = nullptr;
 };

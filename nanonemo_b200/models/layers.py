@@ -180,7 +180,7 @@ class MLP(nn.Module):
             full = self.tp.gather_tokens(x)
             return self.tp.scatter_tokens(self.w_down(ops.swiglu_packed(self.w_gu(full), impl=self.act_impl)))
         if self.fused and x.is_cuda and ops.fused_ok():
-            return self.w_down(ops.linear_swiglu(x, self.w_gu.weight))
+            return ops.mlp_swiglu(x, self.w_gu.weight, self.w_down.weight)
         return self.w_down(ops.swiglu_packed(self.w_gu(x), impl=self.act_impl))
 
 

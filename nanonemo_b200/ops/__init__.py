@@ -244,6 +244,19 @@ def linear_swiglu(x, weight):
     return library.gemm_swiglu(x2, weight)[1].view(*x.shape[:-1], weight.shape[0] // 2)
 
 
+def mlp_swiglu(x, w_gu, w_down):
+    """The SwiGLU feed-forward down(silu(gate(x)) * up(x)) (sm100 only). On the trainer's engine (weights with a 16-bit
+    shadow) it is one autograd node whose backward computes the activation's backward in a GEMM epilogue; elsewhere it is
+    the registered gate||up operator followed by the registered linear."""
+    _need_cuda(x, "mlp_swiglu")
+    engine = lambda w: in_flat_store(w) or getattr(w, "_shadow", None) is not None
+    if engine(w_gu) and engine(w_down) and getattr(w_gu, "_gather_in_gemm", None) is None:
+        from nanonemo_b200.ops.fused_block import mlp_swiglu as f
+
+        return f(x, w_gu, w_down)
+    return linear(linear_swiglu(x, w_gu), w_down, impl="sm100")
+
+
 def embedding(idx, weight, impl="torch"):
     if impl == "torch":
         return F.embedding(idx, weight)

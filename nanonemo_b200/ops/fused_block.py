@@ -8,6 +8,11 @@ backward (csrc/flash_bwd.cu) instead of being a pass over HBM of its own:
 ``linear_swiglu(x, w_gu)``
     gate||up projection whose epilogue also writes ``silu(gate) * up``; the projection is kept for backward, which
     recomputes the sigmoid from it (as nanonemo/kernels/triton/swiglu.py:45-66 does).
+``mlp_swiglu(x, w_gu, w_down)``
+    the whole feed-forward as one autograd node, so that the backward of the activation can ride in the epilogue of the
+    down projection's input-gradient GEMM: d(gate) | d(up) leave tensor memory directly and the gradient of the
+    activation is never written to HBM (the reference runs linear backward, then the SwiGLU backward kernel,
+    nanonemo/kernels/triton/swiglu.py:45-90).
 
 Each falls back, operator by operator, to the plain GEMM followed by the stand-alone kernel when the CTA-pair GEMM does
 not serve the shape (fewer than 256 rows, d_ff not a multiple of 128, head_dim other than 64 / 128), so results do not
@@ -20,7 +25,8 @@ import os
 import torch
 
 from nanonemo_b200.ops import attention, rope, swiglu_act
-from nanonemo_b200.ops.gemm import _rowmajor2d, compute_dtype, gemm, gemm_rope, gemm_swiglu, linear_backward, shadow_of
+from nanonemo_b200.ops.gemm import (_rowmajor2d, compute_dtype, gemm, gemm_rope, gemm_swiglu, gemm_swiglu_bwd, linear_backward,
+                                    shadow_of)
 
 
 def _rows16(x, dt):
@@ -132,3 +138,50 @@ class _LinearSwiGLU(torch.autograd.Function):
 def linear_swiglu(x, weight):
     """x: (..., d); weight: [2 F, d], gate rows first -> silu(x Wg^T) * (x Wu^T), shape (..., F)."""
     return _LinearSwiGLU.apply(x, weight)
+
+
+FUSE_SWIGLU_BWD = os.environ.get("NANONEMO_FUSE_SWIGLU_BWD", "1") != "0"
+
+
+class _MLPSwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down):
+        dt = compute_dtype()
+        w16_gu, w16_down = shadow_of(w_gu, dt), shadow_of(w_down, dt)
+        x2 = _rows16(x, dt)
+        F = w_gu.shape[0] // 2
+        fused = gemm_swiglu(x2, w16_gu)
+        if fused is None:
+            gu = gemm(x2, w16_gu)
+            act = torch.empty((x2.shape[0], F), dtype=dt, device=x.device)
+            swiglu_act.fwd_raw(gu[:, :F], gu[:, F:], act)
+        else:
+            gu, act = fused
+        y = gemm(act, w16_down)
+        ctx.save_for_backward(x2, w_gu, w_down, gu, act)
+        ctx.w16, ctx.x_shape, ctx.x_dtype = (w16_gu, w16_down), x.shape, x.dtype
+        return y.view(*x.shape[:-1], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_gu, w_down, gu, act = ctx.saved_tensors
+        w16_gu, w16_down = ctx.w16
+        F = gu.shape[1] // 2
+        dy2 = _rows16(dy, gu.dtype)
+        dgu = gemm_swiglu_bwd(dy2, w16_down, gu) if FUSE_SWIGLU_BWD else None
+        if dgu is None:
+            dact = gemm(dy2, w16_down, b_mn=True)
+            dgu = torch.empty_like(gu)
+            swiglu_act.bwd_raw(dact, gu[:, :F], gu[:, F:], dgu[:, :F], dgu[:, F:])
+        _, dw_down = linear_backward(dy2, act, w_down, w16_down, False, ctx.needs_input_grad[2])
+        dx, dw_gu = linear_backward(dgu, x2, w_gu, w16_gu, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        if dx is not None:
+            dx = dx.view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        return dx, dw_gu, dw_down
+
+
+def mlp_swiglu(x, w_gu, w_down):
+    """x: (..., d); w_gu: [2 F, d] (gate rows first); w_down: [d, F] -> down(silu(x Wg^T) * (x Wu^T)), shape (..., d)."""
+    return _MLPSwiGLU.apply(x, w_gu, w_down)

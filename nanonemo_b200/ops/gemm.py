@@ -92,6 +92,22 @@ def gemm_swiglu(x2: torch.Tensor, w_gu: torch.Tensor):
     return (gu, act) if ok else None
 
 
+def gemm_swiglu_bwd(dy2: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor):
+    """SwiGLU backward inside the down projection's input-gradient GEMM: dy2 [M, d] @ w_down [d, F] is the gradient of
+    act = silu(gate) * up; the epilogue reads the saved projection gu [M, 2F] and writes d(gate) | d(up) [M, 2F] directly
+    (the gradient of act is never stored) -> dgu or None when the CTA-pair kernel does not serve the shape."""
+    M, K = dy2.shape
+    F = w_down.shape[1]
+    if (M < 256 or F < 128 or F % 64 or gu.shape != (M, 2 * F) or gu.stride(1) != 1 or gu.stride(0) % 8 or w_down.stride(1) != 1
+            or dy2.stride(1) != 1 or gu.dtype != dy2.dtype or w_down.dtype != dy2.dtype):
+        return None
+    dgu = torch.empty((M, 2 * F), dtype=gu.dtype, device=gu.device)
+    ok = _fused_call("nnb_gemm_swiglu_bwd", _lib.ptr(dy2), _lib.ptr(w_down), _lib.ptr(gu), _lib.ptr(dgu), _lib.i32(M), _lib.i32(F),
+                     _lib.i32(K), _lib.i64(dy2.stride(0)), _lib.i64(w_down.stride(0)), _lib.i64(gu.stride(0)), _lib.i64(2 * F),
+                     _lib.i32(_CODE[dy2.dtype]), _lib.ptr(status_tensor(dy2.device)), _lib.vp(_lib.stream_ptr()))
+    return dgu if ok else None
+
+
 def gemm_rope(x2: torch.Tensor, w: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, t_len: int, rope_cols: int, head_dim: int):
     """x2 [M, K] @ w [N, K]^T with rotate-half RoPE on columns [0, rope_cols) in the epilogue (row m at position
     m % t_len; cos / sin fp32 [t_len, head_dim / 2] contiguous) -> [M, N] or None."""

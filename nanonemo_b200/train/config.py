@@ -86,6 +86,21 @@ class TrainConfig:
         if self.parallel == "fsdp_tp" and not self.tp_size:
             raise ValueError("parallel=fsdp_tp needs tp_size")
 
+    def inert_settings(self, model_uses_sm100: bool = True) -> list[str]:
+        """Settings of the reference's schema that are accepted (its YAML files load unchanged) but change nothing here, each with
+        the reason; the trainer logs them once at start so that a run never silently differs from what its config says."""
+        notes = []
+        if self.ddp_grad_as_bucket_view:
+            notes.append("ddp_grad_as_bucket_view: gradients are ALWAYS views of the flat bucket buffer here (parallel/flat.py)")
+        if self.fsdp_compile_blocks:
+            notes.append("fsdp_compile_blocks: blocks run hand-written kernels, there is nothing for a per-block compiler to fuse")
+        if self.fp8_recipe != "mxfp8" and self.precision == "fp8":
+            notes.append(f"fp8_recipe={self.fp8_recipe}: every recipe maps to MXFP8 block scaling (no amax history is kept)")
+        if self.compile in ("default", "max-autotune") and model_uses_sm100:
+            notes.append(f"compile={self.compile}: skipped on the sm100 kernel path (the step is already a fixed kernel sequence); "
+                         "use cuda_graph / compile=reduce-overhead to remove launch gaps")
+        return notes
+
     @property
     def checkpointing(self) -> bool:
         return bool(self.ckpt_every or self.stop_after_min or self.max_steps or self.resume_from)

@@ -251,7 +251,8 @@ def train(model_cfg: ModelConfig, cfg: TrainConfig, device: str | None = None,
          "grad_accum": accum, "total_steps": total_steps, "warmup_steps": cfg.warmup_steps,
          "parallel": cfg.parallel, "world": d.world, "start_step": start_step, "resumed_from": resumed_from,
          "kernels": {k: getattr(model_cfg.resolved(), k) for k in
-                     ("norm_kernel", "swiglu_kernel", "rope_kernel", "attn_kernel", "loss_kernel", "linear_impl")}})
+                     ("norm_kernel", "swiglu_kernel", "rope_kernel", "attn_kernel", "loss_kernel", "linear_impl")},
+         "inert_settings": cfg.inert_settings(any(model_cfg.uses_sm100(k) for k in ("norm_kernel", "attn_kernel", "linear_impl")))})
 
     t_session = t_last = time.perf_counter()
     last_logged = start_step - 1

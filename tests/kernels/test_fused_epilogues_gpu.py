@@ -177,3 +177,56 @@ def test_model_same_loss_and_gradients_with_and_without_fused_epilogues(shape):
     for n, g in out[True][1].items():
         ref = out[False][1][n]
         assert (g - ref).norm().item() <= 2e-2 * ref.norm().item() + 1e-8, n
+
+
+@pytest.mark.parametrize("M,F_,K", [(256, 128, 64), (512, 256, 768), (1000, 512, 264), (4096, 2048, 768), (384, 5632, 128), (640, 192, 96)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_swiglu_backward_epilogue(M, F_, K, dtype):
+    """d(gate) | d(up) written by the epilogue of dy @ W_down against fp32 math on the same (rounded) saved projection."""
+    from nanonemo_b200.ops.gemm import check_status, gemm_swiglu_bwd
+
+    torch.manual_seed(M + F_ + K)
+    dy = torch.randn(M, K, device=DEV).to(dtype)
+    w_down = (torch.randn(K, F_, device=DEV) / math.sqrt(K)).to(dtype)  # [d_model, d_ff] as the layer stores it
+    gu = torch.randn(M, 2 * F_, device=DEV).to(dtype)
+    dgu = gemm_swiglu_bwd(dy, w_down, gu)
+    check_status()
+    assert dgu is not None and dgu.shape == (M, 2 * F_)
+    dact = dy.float() @ w_down.float()
+    g, u = gu.float().split(F_, dim=1)
+    s = torch.sigmoid(g)
+    _close(dgu[:, :F_], dact * u * s * (1 + g * (1 - s)))
+    _close(dgu[:, F_:], dact * g * s)
+    # twice in a row: the staging pairs and their barriers carry over from tile to tile and from launch to launch
+    assert torch.equal(dgu, gemm_swiglu_bwd(dy, w_down, gu))
+
+
+def test_mlp_node_matches_unfused_composition():
+    """The one-node feed-forward (SwiGLU backward inside the down projection's dgrad) against linear -> swiglu -> linear built
+    from the separate operators, and against fp32 PyTorch: output, input gradient and both weight gradients."""
+    from nanonemo_b200.ops import fused_block
+    from nanonemo_b200.ops.gemm import check_status
+
+    torch.manual_seed(11)
+    M, d, F_ = 1024, 256, 512
+    x = torch.randn(4, M // 4, d, device=DEV).bfloat16().requires_grad_()
+    w_gu = (torch.randn(2 * F_, d, device=DEV) / math.sqrt(d)).requires_grad_()
+    w_down = (torch.randn(d, F_, device=DEV) / math.sqrt(F_)).requires_grad_()
+    g_out = torch.randn(4, M // 4, d, device=DEV).bfloat16()
+    results = {}
+    for fused in (True, False):
+        fused_block.FUSE_SWIGLU_BWD = fused
+        for t in (x, w_gu, w_down):
+            t.grad = None
+        y = fused_block.mlp_swiglu(x, w_gu, w_down)
+        y.backward(g_out)
+        check_status()
+        results[fused] = (y.detach().clone(), x.grad.clone(), w_gu.grad.clone(), w_down.grad.clone())
+    fused_block.FUSE_SWIGLU_BWD = True
+    xr, wgr, wdr = (t.detach().float().requires_grad_() for t in (x, w_gu.bfloat16(), w_down.bfloat16()))
+    gate, up = (xr @ wgr.t()).split(F_, dim=-1)
+    ref = (F.silu(gate) * up) @ wdr.t()
+    ref.backward(g_out.float())
+    for got_f, got_u, want in zip(results[True], results[False], (ref, xr.grad, wgr.grad, wdr.grad)):
+        _close(got_f, want, tol=3e-2)
+        _close(got_f, got_u, tol=2e-2)

@@ -106,3 +106,14 @@ def test_flat_store_keeps_parameters_and_state_views():
         assert pb.data_ptr() >= store.master.data_ptr() and pb.grad.data_ptr() >= store.grad.data_ptr()
     st = opt_b.state[b.blocks[0].attn.wo.weight]
     assert st["exp_avg"].data_ptr() >= store.exp_avg.data_ptr() and float(st["step"]) == 3
+
+
+def test_accepted_settings_without_effect_are_reported():
+    from nanonemo_b200.train.config import TrainConfig
+
+    assert TrainConfig().inert_settings() == []
+    notes = TrainConfig(parallel="ddp", ddp_grad_as_bucket_view=True, compile="default").inert_settings()
+    assert any(n.startswith("ddp_grad_as_bucket_view") for n in notes) and any(n.startswith("compile=default") for n in notes)
+    assert TrainConfig(compile="default").inert_settings(model_uses_sm100=False) == []
+    notes = TrainConfig(parallel="fsdp", fsdp_compile_blocks=True, precision="fp8").inert_settings()
+    assert any(n.startswith("fsdp_compile_blocks") for n in notes) and any(n.startswith("fp8_recipe=delayed") for n in notes)
