@@ -776,8 +776,9 @@ extern "C" int nnb_gemm_swiglu_bwd(const void* dY, const void* Wdown, const void
   return nnb_gemm2_launch(g, st);
 }
 
-// logits[M, N] = x[M, K] @ w[N, K]^T (16-bit) plus stats[M, ceil(N / 256), 2] = (max, sum of exp(x - max)) of every
-// 256-column tile of every row, computed on the stored (rounded) logits. N must be a multiple of 64.
+// logits[M, N] = x[M, K] @ w[N, K]^T (16-bit) plus stats[M, 2 ceil(N / 256), 2] = (max, sum of exp(x - max)) of every row in
+// two parts per 256-column tile (its even and its odd 64-column chunks), computed on the stored (rounded) logits; a part
+// without columns holds (-inf, 0). N must be a multiple of 64.
 extern "C" int nnb_gemm_ce_stats(const void* X, const void* W, void* logits, void* stats, int M, int N, int K, long long lda,
                                  long long ldw, long long ldd, int dtype, void* status, cudaStream_t st) {
   NnbGemm2Args g{};

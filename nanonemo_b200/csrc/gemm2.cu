@@ -49,7 +49,8 @@ template <int EPI> struct Cfg {
   // Epilogue groups of four warps. The SwiGLU backward does the most arithmetic per accumulator element (a sigmoid and both
   // products, operands read from shared memory): two groups take alternate 64-column chunks, each with its own staging
   // pair, barrier and elected thread, so one group's stores and loads overlap the other's arithmetic.
-  static constexpr int kEpiGroups = EPI == EPI_SWIGLU_BWD ? 2 : 1;
+  // The softmax statistics (an exponential per logit) get the same split, one staging tile per group.
+  static constexpr int kEpiGroups = (EPI == EPI_SWIGLU_BWD || EPI == EPI_CE_STATS) ? 2 : 1;
   static constexpr int kThreads = 64 + kEpiGroups * kEpilogueThreads;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
@@ -66,7 +67,8 @@ struct Params2 {
   int t_len, half_dim; // EPI_ROPE: sequence length (row m uses table row m % t_len), head_dim / 2
   const float* cos_t;  // EPI_ROPE: [t_len, half_dim] fp32
   const float* sin_t;
-  float* stats;        // EPI_CE_STATS: [M, n_blocks, 2] fp32 (max, sum of exp(x - max)) per 256-column tile
+  float* stats;        // EPI_CE_STATS: [M, 2 n_blocks, 2] fp32 (max, sum of exp(x - max)): two entries per 256-column tile (64-column
+                       // chunks 0, 2 and 1, 3 of the tile: one entry per epilogue warp group; (-inf, 0) when the group had no chunk)
 };
 
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf) {
@@ -508,13 +510,18 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       } else {
         const int cols_per_chunk = p.out_f32 ? 32 : 64;
         const int chunks = BN / cols_per_chunk;
-        float st_m = -INFINITY, st_s = 0.f;  // EPI_CE_STATS: this row's running (max, sum of exp) over the tile
-        for (int c = 0; c < chunks && rows_live; ++c) {
+        constexpr int G = Cfg<EPI>::kEpiGroups;  // with two groups: group g takes chunks g, g + 2 through staging tile g
+        float st_m = -INFINITY, st_s = 0.f;  // EPI_CE_STATS: this row's running (max, sum of exp) over the group's chunks of the tile
+        for (int c = (G == 2 ? grp : 0); c < chunks && rows_live; c += G) {
           const int col0 = c * cols_per_chunk;
           if (n_blk * BN + col0 >= p.N) break;
-          uint8_t* buf = staging + (gchunk & 1) * (BM * 128);
+          uint8_t* buf = staging + (G == 2 ? grp : (int)(gchunk & 1)) * (BM * 128);
           ++gchunk;
-          if (et == 0 && pending_stores >= 2) tma_wait_group_read<1>();
+          if (G == 2) {
+            if (et == 0 && pending_stores >= 1) tma_wait_group_read<0>();
+          } else if (et == 0 && pending_stores >= 2) {
+            tma_wait_group_read<1>();
+          }
           named_barrier_sync(epi_bar, kEpilogueThreads);
           uint8_t* my_row = buf + row * 128;
           if (p.out_f32) {
@@ -563,7 +570,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
         if constexpr (EPI == EPI_CE_STATS) {
           if (rows_live && d_row + row < p.M)
-            *reinterpret_cast<float2*>(p.stats + ((size_t)(d_row + row) * p.n_blocks + n_blk) * 2) = make_float2(st_m, st_s);
+            *reinterpret_cast<float2*>(p.stats + (((size_t)(d_row + row) * p.n_blocks + n_blk) * G + grp) * 2) = make_float2(st_m, st_s);
         }
       }
       // this CTA's half of the accumulator has been read: tell the leader's MMA thread

@@ -24,7 +24,8 @@ struct NnbGemm2Args {
   int t_len = 0, rope_cols = 0, head_dim = 0;
   // EPI_SWIGLU_BWD: the product [M, N = F] is the gradient of act = silu(gate) * up; E = the saved projection gate||up
   // [M, 2 F] (row stride lde), D = its gradient [M, 2 F] (row stride ldd); the product itself is never stored
-  // EPI_CE_STATS: fp32 [M, ceil(N / 256), 2] receiving (max, sum of exp(x - max)) of every 256-column tile of every row
+  // EPI_CE_STATS: fp32 [M, 2 ceil(N / 256), 2] receiving (max, sum of exp(x - max)) of every row's logits in two parts per
+  // 256-column tile (the tile's even and odd 64-column chunks); a part without columns holds (-inf, 0)
   void* stats = nullptr;
 };
 

@@ -123,12 +123,13 @@ def gemm_rope(x2: torch.Tensor, w: torch.Tensor, cos: torch.Tensor, sin: torch.T
 
 
 def gemm_ce_stats(x2: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
-    """out [M, N] = x2 @ w^T plus the per-tile softmax statistics -> stats fp32 [M, ceil(N / 256), 2] or None."""
+    """out [M, N] = x2 @ w^T plus partial softmax statistics (max, sum of exp(x - max)) of every row, two parts per
+    256-column tile -> stats fp32 [M, 2 ceil(N / 256), 2] or None."""
     M, K = x2.shape
     N = w.shape[0]
     if M < 256 or N < 128 or N % 64:
         return None
-    stats = torch.empty((M, (N + 255) // 256, 2), dtype=torch.float32, device=x2.device)
+    stats = torch.empty((M, 2 * ((N + 255) // 256), 2), dtype=torch.float32, device=x2.device)
     ok = _fused_call("nnb_gemm_ce_stats", _lib.ptr(x2), _lib.ptr(w), _lib.ptr(out), _lib.ptr(stats), _lib.i32(M), _lib.i32(N),
                      _lib.i32(K), _lib.i64(x2.stride(0)), _lib.i64(w.stride(0)), _lib.i64(out.stride(0)), _lib.i32(_CODE[x2.dtype]),
                      _lib.ptr(status_tensor(x2.device)), _lib.vp(_lib.stream_ptr()))

@@ -79,7 +79,7 @@ def test_gemm_ce_stats_epilogue_and_one_sweep_ce(M, V, K):
     logits = torch.empty(M, V, device=DEV, dtype=torch.bfloat16)
     stats = gemm_ce_stats(x, w, logits)
     check_status()
-    assert stats is not None and stats.shape == (M, (V + 255) // 256, 2)
+    assert stats is not None and stats.shape == (M, 2 * ((V + 255) // 256), 2)  # two parts per 256-column tile
     _close(logits, x.float() @ w.float().t())
     lf = logits.float()
     lse_tiles = stats[..., 0] + stats[..., 1].log()
