@@ -40,17 +40,18 @@ constexpr int BK = 64;
 constexpr int kEpilogueThreads = 128;  // one epilogue GROUP: four warps, one per tensor-memory lane quadrant
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = (BN / 2) * BK * 2, kStageBytes = kStageBytesA + kStageBytesB;
 constexpr int kTmemCols = 512;
-// The SwiGLU epilogue fills three staging tiles at once (gate, up, act), its backward keeps two (gate, up) tile pairs in
-// flight (one being computed on / stored, one being loaded): one stage less for the operand ring.
+// The SwiGLU epilogue fills three staging tiles per 64-feature round (gate, up, act), one round per epilogue group; its
+// backward keeps two (gate, up) tile pairs in flight: both pay for the staging with stages of the operand ring.
 template <int EPI> struct Cfg {
-  static constexpr int kStages = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) ? 5 : 6;
-  static constexpr int kStagingTiles = EPI == EPI_SWIGLU ? 3 : (EPI == EPI_SWIGLU_BWD ? 4 : 2);
+  static constexpr int kStages = EPI == EPI_SWIGLU ? 4 : (EPI == EPI_SWIGLU_BWD ? 5 : 6);
+  static constexpr int kStagingTiles = EPI == EPI_SWIGLU ? 6 : (EPI == EPI_SWIGLU_BWD ? 4 : 2);
   static constexpr int kStagingBytes = kStagingTiles * BM * 128;
   // Epilogue groups of four warps. The SwiGLU backward does the most arithmetic per accumulator element (a sigmoid and both
   // products, operands read from shared memory): two groups take alternate 64-column chunks, each with its own staging
   // pair, barrier and elected thread, so one group's stores and loads overlap the other's arithmetic.
   // The softmax statistics (an exponential per logit) get the same split, one staging tile per group.
-  static constexpr int kEpiGroups = (EPI == EPI_SWIGLU_BWD || EPI == EPI_CE_STATS) ? 2 : 1;
+  // The SwiGLU forward: one 64-feature round (gate | up | act tiles) per group.
+  static constexpr int kEpiGroups = (EPI == EPI_SWIGLU_BWD || EPI == EPI_CE_STATS || EPI == EPI_SWIGLU) ? 2 : 1;
   static constexpr int kThreads = 64 + kEpiGroups * kEpilogueThreads;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
@@ -360,12 +361,13 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         // accumulator columns [0, 128) = gate, [128, 256) = up of features n_blk * 128 ...; 64 features per round, all three
         // staging tiles (gate | up | act) filled in two half rounds of 32 columns, then three TMA stores
         const int F = p.epi_cols;
-        for (int c = 0; c < 2 && rows_live; ++c) {
+        uint8_t* tiles = staging + grp * 3 * (BM * 128);  // this group's gate | up | act staging tiles
+        for (int c = grp; c < 2 && rows_live; c += Cfg<EPI>::kEpiGroups) {
           const int fcol = n_blk * (BN / 2) + c * 64;
           if (fcol >= F) break;
           if (et == 0 && pending_stores > 0) tma_wait_group_read<0>();
           named_barrier_sync(epi_bar, kEpilogueThreads);
-          uint8_t* row_g = staging + row * 128;
+          uint8_t* row_g = tiles + row * 128;
           uint8_t* row_u = row_g + BM * 128;
           uint8_t* row_a = row_u + BM * 128;
 #pragma unroll
@@ -388,9 +390,9 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           fence_proxy_async_smem();
           named_barrier_sync(epi_bar, kEpilogueThreads);
           if (et == 0) {
-            tma_store_2d(&tmD, smem_u32(staging), fcol, d_row);
-            tma_store_2d(&tmD, smem_u32(staging + BM * 128), F + fcol, d_row);
-            tma_store_2d(&tmE, smem_u32(staging + 2 * BM * 128), fcol, d_row);
+            tma_store_2d(&tmD, smem_u32(tiles), fcol, d_row);
+            tma_store_2d(&tmD, smem_u32(tiles + BM * 128), F + fcol, d_row);
+            tma_store_2d(&tmE, smem_u32(tiles + 2 * BM * 128), fcol, d_row);
             tma_commit_group();
           }
           pending_stores = 1;
