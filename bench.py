@@ -65,6 +65,7 @@ def parse():
                     help="layout for N > 1 (the headline number is ddp; fsdp / tp give the other BASELINE configs)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every kernel from the host instead of replaying the micro-batch from a CUDA graph (ddp / single GPU)")
+    ap.add_argument("--bucket-mb", type=float, default=100.0, help="gradient bucket size of the data-parallel all-reduce (MiB)")
     ap.add_argument("--set", nargs="*", default=[], metavar="section.key=value")
     return ap.parse_args()
 
@@ -96,7 +97,7 @@ def run_ours(a):
     dp = 1 if par == "tp" else world  # tensor parallel: one replica = the whole group
     cfg = TrainConfig(data_dir="synthetic", out_dir="runs/bench", seq_len=SEQ_LEN, micro_batch=a.micro_batch,
                       global_batch_tokens=a.micro_batch * SEQ_LEN * dp, total_tokens=10**12, precision="bf16",
-                      parallel=par, ddp_bucket_mb=100.0, fsdp_prefetch=True, eval_every=10**9,
+                      parallel=par, ddp_bucket_mb=a.bucket_mb, fsdp_prefetch=True, eval_every=10**9,
                       cuda_graph=par in ("none", "ddp") and a.kernels == "sm100" and not a.no_graph)
     model_cfg, cfg = apply_overrides(model_cfg, cfg, a.set)
 

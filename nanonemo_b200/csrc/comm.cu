@@ -24,6 +24,7 @@
 //
 // The reference reaches NCCL through torch DDP / FSDP2 / DTensor (nanonemo/distributed/*.py).
 #include <cmath>
+#include <cstdlib>
 
 #include "comm.cuh"
 
@@ -68,41 +69,48 @@ __global__ void __launch_bounds__(kCommThreads, 3) allreduce_f32_kernel(Peers P,
   const long long n4 = (s1 - s0) >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   float ss = 0.f;
-  if (ok) {
+  if (ok && mc != nullptr) {
+    // The switch adds the ranks' values (multimem.ld_reduce) and broadcasts the result (multimem.st): one load and one store
+    // per 16 bytes whatever the world size, so the loads in flight come from unrolling over positions only.
+    constexpr int UM = 8;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * UM) {
+      float4 v[UM];
+#pragma unroll
+      for (int u = 0; u < UM; ++u)
+        if (i0 + u * stride < n4) v[u] = multimem_ld_reduce_f4(mc + lo + s0 + 4 * (i0 + u * stride));
+#pragma unroll
+      for (int u = 0; u < UM; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= n4) continue;
+        float4 acc = v[u];
+        acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        multimem_st_f4(mc + lo + s0 + 4 * i, acc);
+      }
+    }
+  } else if (ok) {
     for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
       float4 v[U][WMAX];
-      if (mc != nullptr) {
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (i0 + u * stride < n4) v[u][0] = multimem_ld_reduce_f4(mc + lo + s0 + 4 * (i0 + u * stride));
-      } else {
+      for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int r = 0; r < WMAX; ++r)
-            if (r < world && i0 + u * stride < n4)
-              v[u][r] = ld_peer_f4(static_cast<const float*>(P.data[r]) + lo + s0 + 4 * (i0 + u * stride));
-      }
+        for (int r = 0; r < WMAX; ++r)
+          if (r < world && i0 + u * stride < n4)
+            v[u][r] = ld_peer_f4(static_cast<const float*>(P.data[r]) + lo + s0 + 4 * (i0 + u * stride));
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
         if (i >= n4) continue;
         const long long off = lo + s0 + 4 * i;
         float4 acc = v[u][0];
-        if (mc == nullptr) {
 #pragma unroll
-          for (int r = 1; r < WMAX; ++r)  // fixed order: the result does not depend on who reduces
-            if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
-        }
+        for (int r = 1; r < WMAX; ++r)  // fixed order: the result does not depend on who reduces
+          if (r < world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
         acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
         ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
-        if (mc != nullptr) {
-          multimem_st_f4(mc + off, acc);
-        } else {
 #pragma unroll
-          for (int r = 0; r < WMAX; ++r)
-            if (r < world) *reinterpret_cast<float4*>(static_cast<float*>(P.data[r]) + off) = acc;
-        }
+        for (int r = 0; r < WMAX; ++r)
+          if (r < world) *reinterpret_cast<float4*>(static_cast<float*>(P.data[r]) + off) = acc;
       }
     }
   }
@@ -111,7 +119,7 @@ __global__ void __launch_bounds__(kCommThreads, 3) allreduce_f32_kernel(Peers P,
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x < 32) {
-      float v = threadIdx.x < kCommThreads / 32 ? s_part[threadIdx.x] : 0.f;
+      float v = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
       v = warp_sum(v);  // fixed tree: the same inputs give the same bits
       const long long slot = ((long long)bucket * world + rank) * slot_blocks + blockIdx.x;
       if ((int)threadIdx.x < world) static_cast<float*>(NP.data[threadIdx.x])[slot] = v;
@@ -219,7 +227,7 @@ __global__ void __launch_bounds__(kCommThreads, 3) reduce_scatter_f32_kernel(Pee
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x < 32) {
-      float v = threadIdx.x < kCommThreads / 32 ? s_part[threadIdx.x] : 0.f;
+      float v = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
       v = warp_sum(v);
       if (threadIdx.x == 0 && sumsq_out != nullptr) atomicAdd(sumsq_out, v);
       if (NP.data[0] != nullptr && (int)threadIdx.x < world)
@@ -407,6 +415,22 @@ extern "C" int nnb_comm_timeout_probe(void* flags, void* status, void* result, i
 // shares them indexes its flag slots with it.
 extern "C" int nnb_comm_flag_words(int blocks) { return 2 * blocks * kMaxWorld; }
 
+// Threads per collective block (a multiple of 32 up to kCommThreads; NANONEMO_COMM_THREADS). The default of 128 keeps a block
+// at about 10 K registers, so that it fits on an SM next to ANY compute kernel of the training step, including the
+// 320-thread x 168-register attention backward and the GEMMs with two epilogue groups (53.8 K of the 64 K registers): a
+// collective that cannot share the SM either waits for those kernels or, once resident, keeps their CTAs off the SM while it
+// sits in a cross-GPU barrier. The launcher's `blocks` (two per SM by default) makes up for the smaller blocks wherever the
+// resident compute kernel leaves room for both.
+static inline int comm_threads() {
+  static int threads = [] {
+    const char* e = getenv("NANONEMO_COMM_THREADS");
+    int t = e ? atoi(e) : 128;
+    t = (t / 32) * 32;
+    return t < 32 ? 32 : (t > kCommThreads ? kCommThreads : t);
+  }();
+  return threads;
+}
+
 static inline unsigned long long timeout_ns_of(double seconds) {
   return seconds > 0 ? (unsigned long long)(seconds * 1e9) : kDefaultTimeoutNs;
 }
@@ -426,9 +450,9 @@ extern "C" int nnb_allreduce_f32(void* const* data_ptrs, void* const* flag_ptrs,
   int* stw = static_cast<int*>(status);
   uint32_t* ep = static_cast<uint32_t*>(epochs);
   const unsigned long long tns = timeout_ns_of(timeout_s);
-  if (world <= 2) allreduce_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
-  else if (world <= 4) allreduce_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
-  else allreduce_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
+  if (world <= 2) allreduce_f32_kernel<2, 4><<<blocks, comm_threads(), 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
+  else if (world <= 4) allreduce_f32_kernel<4, 2><<<blocks, comm_threads(), 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
+  else allreduce_f32_kernel<8, 1><<<blocks, comm_threads(), 0, st>>>(P, NP, mc, rank, world, lo, n, scale, ep, blocks, bucket, tns, stw);
   NNB_LAUNCH_OK("allreduce_f32");
   return 0;
 }
@@ -456,9 +480,9 @@ static int launch_reduce_scatter(void* const* data_ptrs, void* const* flag_ptrs,
   int* stw = static_cast<int*>(status);
   uint32_t* ep = static_cast<uint32_t*>(epochs);
   const unsigned long long tns = timeout_ns_of(timeout_s);
-  if (world <= 2) reduce_scatter_f32_kernel<2, 4><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
-  else if (world <= 4) reduce_scatter_f32_kernel<4, 2><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
-  else reduce_scatter_f32_kernel<8, 1><<<blocks, kCommThreads, 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
+  if (world <= 2) reduce_scatter_f32_kernel<2, 4><<<blocks, comm_threads(), 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
+  else if (world <= 4) reduce_scatter_f32_kernel<4, 2><<<blocks, comm_threads(), 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
+  else reduce_scatter_f32_kernel<8, 1><<<blocks, comm_threads(), 0, st>>>(P, NP, o, sq, rank, world, lo, per, scale, ep, blocks, bucket, A, tns, stw);
   NNB_LAUNCH_OK("reduce_scatter_f32");
   return 0;
 }
@@ -498,7 +522,7 @@ extern "C" int nnb_allgather_bytes(void* const* data_ptrs, void* const* flag_ptr
   NNB_REQUIRE(src_off % 16 == 0 && per_bytes % 16 == 0 && nnb_aligned16(local_full), "allgather: 16-byte alignment required");
   NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr, "allgather: bad block count %d or no epoch counters", blocks);
   if (per_bytes == 0) return 0;
-  allgather_kernel<<<blocks, kCommThreads, 0, st>>>(P, static_cast<uint8_t*>(local_full), rank, world, src_off, per_bytes,
+  allgather_kernel<<<blocks, comm_threads(), 0, st>>>(P, static_cast<uint8_t*>(local_full), rank, world, src_off, per_bytes,
                                                     static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
                                                     static_cast<int*>(status));
   NNB_LAUNCH_OK("allgather");
@@ -514,7 +538,7 @@ extern "C" int nnb_peer_fetch(void* const* data_ptrs, void* const* flag_ptrs, co
   NNB_REQUIRE(blocks > 0 && blocks <= 1024 && epochs != nullptr && items != nullptr, "peer_fetch: bad arguments");
   if (n_items <= 0) return 0;
   static_assert(sizeof(FetchItem) == 32, "FetchItem layout is part of the interface");
-  peer_fetch_kernel<<<min(n_items, blocks), kCommThreads, 0, st>>>(P, static_cast<const FetchItem*>(items), n_items, rank, world,
+  peer_fetch_kernel<<<min(n_items, blocks), comm_threads(), 0, st>>>(P, static_cast<const FetchItem*>(items), n_items, rank, world,
                                                                   static_cast<uint32_t*>(epochs), blocks, timeout_ns_of(timeout_s),
                                                                   static_cast<int*>(status));
   NNB_LAUNCH_OK("peer_fetch");
@@ -540,7 +564,7 @@ extern "C" int nnb_vp_embedding_fwd(void* const* stage_ptrs, void* const* flag_p
   if (fill_peers(P, stage_ptrs, flag_ptrs, world) != 0) return -1;
   if (vp_embed_checks("vp_embedding_fwd", idx, W, out, per, D, V, blocks, epochs) != 0) return -1;
   NNB_DISPATCH(dtype, TO, {
-    vp_embed_fwd_kernel<TO><<<blocks, kCommThreads, 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const float*>(W), static_cast<TO*>(out),
+    vp_embed_fwd_kernel<TO><<<blocks, comm_threads(), 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const float*>(W), static_cast<TO*>(out),
                                                             per, D, v0, V, rank, world, static_cast<uint32_t*>(epochs), blocks,
                                                             timeout_ns_of(timeout_s), static_cast<int*>(status));
   });
@@ -555,7 +579,7 @@ extern "C" int nnb_vp_embedding_bwd(void* const* stage_ptrs, void* const* flag_p
   if (fill_peers(P, stage_ptrs, flag_ptrs, world) != 0) return -1;
   if (vp_embed_checks("vp_embedding_bwd", idx, dW, g, per, D, V, blocks, epochs) != 0) return -1;
   NNB_DISPATCH(dtype, TO, {
-    vp_embed_bwd_kernel<TO><<<blocks, kCommThreads, 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const TO*>(g), static_cast<float*>(dW),
+    vp_embed_bwd_kernel<TO><<<blocks, comm_threads(), 0, st>>>(P, static_cast<const long long*>(idx), static_cast<const TO*>(g), static_cast<float*>(dW),
                                                             per, D, v0, V, rank, world, static_cast<uint32_t*>(epochs), blocks,
                                                             timeout_ns_of(timeout_s), static_cast<int*>(status));
   });

@@ -12,9 +12,9 @@ constexpr int kMaxWorld = 16;
 // enough that a peer that has gone away ends the kernel instead of hanging the GPU. A poll-count bound can be added on top
 // (the bounded-wait test uses a few thousand polls).
 constexpr unsigned long long kDefaultTimeoutNs = 30ull * 1000000000ull;
-// 256 threads and at most 85 registers: a collective block then fits on an SM BESIDE a resident GEMM or attention CTA
-// (192..320 threads, <= 168 registers), so a collective running on the side stream neither waits for a persistent GEMM to
-// drain nor takes SMs away from it.
+// At most 256 threads (the launchers use 128 by default, see comm_threads() in comm.cu) and at most 85 registers: a collective
+// block then fits on an SM BESIDE a resident GEMM or attention CTA, so a collective running on the side stream neither waits
+// for a persistent GEMM to drain nor takes SMs away from it.
 constexpr int kCommThreads = 256;
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {

@@ -64,9 +64,10 @@ class SymmetricComm:
         from nanonemo_b200.ops import _lib
 
         self.rank, self.world, self.group = rank, world, group
-        # one block per SM: 256-thread, <= 85-register blocks that share an SM with whatever compute kernel is resident
+        # two light blocks per SM (128 threads, <= 85 registers each: csrc/comm.cu comm_threads()): one always fits beside whatever
+        # compute kernel is resident, both fit beside the plain GEMMs
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", str(sms)))
+        self.blocks = blocks or int(os.environ.get("NANONEMO_COMM_BLOCKS", str(2 * sms)))
         words = _lib.lib().nnb_comm_flag_words(self.blocks)
         self.flags = SymmetricBuffer(words, torch.int32, device, group)
         self.flags.tensor.zero_()
@@ -187,10 +188,38 @@ class SymmetricAllReduce:
         self.comm = SymmetricComm(data.tensor.device, group, data.rank, data.world)
         if with_norm:
             self.comm.enable_norm_parts()
-        self.use_multimem = bool(data.multicast_ptr) and os.environ.get("NANONEMO_MULTIMEM", "0") == "1"
+        # NVSwitch multicast (multimem.ld_reduce / multimem.st): the switch does the sum, so a rank moves the data once instead of
+        # 2 (N - 1) / N times. Opt-in (NANONEMO_MULTIMEM=1): with two ranks the plain path is faster (a single peer load already
+        # is the whole reduction), with four it measured equal in isolation (1.03 vs 1.05 ms for 435 MiB) and inside the
+        # training step (35.6 vs 35.6-35.8 ms). When asked for, it is used only after a small all-reduce through the multicast
+        # address has given the exact expected values on every rank.
+        want = os.environ.get("NANONEMO_MULTIMEM", "0")
+        self.use_multimem = bool(data.multicast_ptr) and want == "1" and self._multicast_gives_exact_sums(group)
 
     def all_reduce_(self, lo: int, hi: int, scale: float, bucket: int = -1):
         self.comm.all_reduce_(self.data, lo, hi, scale, self.use_multimem, bucket)
+
+    def _multicast_gives_exact_sums(self, group) -> bool:
+        """One all-reduce of the buffer's first elements through the multicast address, on small integers (exact in any order);
+        the elements are put back afterwards. False on any rank -> False on all (the plain peer-load path is used)."""
+        t, world, rank = self.data.tensor, self.data.world, self.data.rank
+        n = min(t.numel(), 4096 * world) // (4 * world) * (4 * world)
+        if n == 0:
+            return False
+        keep = t[:n].clone()
+        base = (torch.arange(n, device=t.device) % 13).float()
+        t[:n] = base + rank
+        torch.cuda.synchronize(t.device)
+        dist.barrier(group)
+        self.comm.all_reduce_(self.data, 0, n, 1.0, True, -1)
+        good = torch.equal(t[:n], base * world + sum(range(world))) and int(self.comm.status[0].item()) == 0
+        self.comm.status.zero_()
+        torch.cuda.synchronize(t.device)
+        dist.barrier(group)
+        t[:n] = keep
+        flag = torch.tensor([1 if good else 0], device=t.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        return bool(flag.item())
 
     def norm_sq(self, n_buckets: int) -> torch.Tensor:
         return self.comm.norm_sq(n_buckets)

@@ -1,15 +1,24 @@
 #!/usr/bin/env python
 """Where a training step spends its GPU time: kernel time per group from the PyTorch profiler (CUDA activity only).
 
-    python scripts/step_breakdown.py --config configs/b200/single.yaml [--steps 3] [--set train.micro_batch=32]
+    python scripts/step_breakdown.py --config configs/b200/single.yaml [--steps 3] [--set train.micro_batch=32] [--timeline]
+    python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc_per_node=2 scripts/step_breakdown.py \
+        --config configs/b200/ddp.yaml --timeline
 
 Prints one row per kernel group (GEMMs, attention forward / backward, norms, SwiGLU, RoPE, cross-entropy, optimizer,
 collectives, everything else) with milliseconds per step and the share of the total. Times come from the profiler's kernel
 records, so they add up to busy GPU time, not to wall-clock step time.
+
+With --timeline the kernel records are also laid out in time (from the profiler's trace): wall time per step, busy time of the
+compute stream, its largest idle gaps with the kernels on either side, and for the collective kernels how much of their run
+time fell into such gaps, i.e. was EXPOSED rather than hidden under compute (the reference's scripts/nsys_comm.py reports only
+the share of kernel time that is communication, not whether it overlapped).
 """
 
 import argparse
+import json
 import sys
+import tempfile
 from collections import defaultdict
 from pathlib import Path
 
@@ -40,6 +49,49 @@ def group_of(name: str) -> str:
     return "other"
 
 
+COLLECTIVE_KEYS = ("allreduce", "reduce_scatter", "allgather", "all_gather", "nccl", "vp_embed", "peer_fetch", "sumsq_combine")
+
+
+def timeline_report(trace_events: list, steps: int, top: int = 8) -> list[str]:
+    """Lines describing how one rank's kernels were laid out in time. `trace_events`: the chrome-trace records of the
+    profiler (dicts with ph == "X", cat == "kernel", ts / dur in microseconds and args.stream)."""
+    kernels = sorted(({"name": e["name"], "t0": float(e["ts"]), "t1": float(e["ts"]) + float(e["dur"]), "stream": e.get("args", {}).get("stream", 0)}
+                      for e in trace_events if e.get("ph") == "X" and e.get("cat") == "kernel"), key=lambda k: k["t0"])
+    if not kernels:
+        return ["no kernel records in the trace"]
+    busy_by_stream = defaultdict(float)
+    for k in kernels:
+        busy_by_stream[k["stream"]] += k["t1"] - k["t0"]
+    main_stream = max(busy_by_stream, key=busy_by_stream.get)
+    comp = [k for k in kernels if k["stream"] == main_stream]
+    wall = kernels[-1]["t1"] - kernels[0]["t0"]
+    # idle intervals of the compute stream (merged coverage, then the holes)
+    gaps, edge = [], comp[0]["t1"]
+    prev = comp[0]
+    for k in comp[1:]:
+        if k["t0"] > edge:
+            gaps.append((edge, k["t0"], prev["name"], k["name"]))
+        if k["t1"] > edge:
+            edge, prev = k["t1"], k
+    idle = sum(b - a for a, b, _, _ in gaps)
+    coll = [k for k in kernels if any(key in k["name"].lower() for key in COLLECTIVE_KEYS)]
+    coll_busy = sum(k["t1"] - k["t0"] for k in coll)
+    exposed = 0.0
+    for k in coll:
+        for a, b, _, _ in gaps:
+            lo, hi = max(a, k["t0"]), min(b, k["t1"])
+            if hi > lo:
+                exposed += hi - lo
+    ms = lambda us: us / 1e3 / steps
+    out = [f"timeline ({steps} steps, this rank): wall {ms(wall):.2f} ms / step | compute stream busy {ms(busy_by_stream[main_stream]):.2f} | "
+           f"compute stream idle {ms(idle):.2f} | collective kernels {ms(coll_busy):.2f} of which exposed (compute stream idle) {ms(exposed):.2f}",
+           f"largest idle gaps of the compute stream (us, whole window):"]
+    for a, b, before, after in sorted(gaps, key=lambda g: g[0] - g[1])[:top]:
+        during = sorted({k["name"][:40] for k in kernels if k["stream"] != main_stream and k["t0"] < b and k["t1"] > a})
+        out.append(f"  {b - a:8.1f}  after {before[:48]} | before {after[:48]} | other streams: {', '.join(during) or '-'}")
+    return out
+
+
 def main(argv=None):
     import torch
     from torch.profiler import ProfilerActivity, profile
@@ -54,6 +106,7 @@ def main(argv=None):
     ap.add_argument("--config", required=True)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--set", nargs="*", default=[], metavar="section.key=value")
+    ap.add_argument("--timeline", action="store_true", help="also report idle gaps of the compute stream and exposed collective time")
     a = ap.parse_args(argv)
     model_cfg, cfg = apply_overrides(*load_config(a.config), a.set)
     d = parallel.init()
@@ -87,6 +140,13 @@ def main(argv=None):
         print("\ntop kernels:")
         for name, ms in sorted(per_kernel.items(), key=lambda kv: -kv[1])[:12]:
             print(f"  {ms:7.3f} ms  {name[:110]}")
+        if a.timeline:
+            with tempfile.TemporaryDirectory() as tmp:
+                path = Path(tmp) / "trace.json"
+                prof.export_chrome_trace(str(path))
+                events = json.loads(path.read_text()).get("traceEvents", [])
+            print()
+            print("\n".join(timeline_report(events, a.steps)))
     parallel.destroy()
 
 

@@ -78,3 +78,19 @@ def test_step_breakdown_groups_kernel_names():
     assert mod.group_of("void add_rmsnorm_bwd_kernel<float, __nv_bfloat16, __nv_bfloat16, 3>") == "add + RMSNorm"
     assert mod.group_of("ncclDevKernel_AllReduce_Sum_f32_RING_LL") == "collectives"
     assert mod.group_of("something_else") == "other"
+
+
+def test_timeline_report_finds_gaps_and_exposed_collective_time():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("step_breakdown", ROOT / "scripts" / "step_breakdown.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    k = lambda name, ts, dur, stream: {"ph": "X", "cat": "kernel", "name": name, "ts": ts, "dur": dur, "args": {"stream": stream}}
+    # compute stream 7: busy 0-100, idle 100-150, busy 150-250; an all-reduce on stream 9 runs 80-140 (40 us of it in the gap)
+    events = [k("gemm2_tcgen05_kernel<0>", 0, 100, 7), k("adamw_flat_kernel", 150, 100, 7), k("allreduce_f32_kernel<2, 4>", 80, 60, 9),
+              {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "ts": 0, "dur": 5}]
+    lines = mod.timeline_report(events, steps=1)
+    assert "wall 0.25 ms / step" in lines[0] and "compute stream busy 0.20" in lines[0] and "compute stream idle 0.05" in lines[0]
+    assert "collective kernels 0.06 of which exposed (compute stream idle) 0.04" in lines[0]
+    assert "50.0" in lines[2] and "allreduce_f32_kernel" in lines[2]
