@@ -7,7 +7,7 @@
 #   NCU_COUNT=24 NCU_ITERS=2 benchmarks/kernels/ncu.sh rope,embedding,quantize 'regex:rope_packed|embedding_|quantize' out_dir small
 # (NCU_COUNT launches matching the pattern, after NCU_SKIP of them; NCU_ITERS calls of each target).
 set -euo pipefail
-target=${1:?target: gemm|gemm_single|gemm_mxfp8|gemm_swiglu|gemm_rope|flash|flash128|rmsnorm|swiglu|rope|ce|adamw|embedding|quantize}
+target=${1:?target: gemm|gemm_single|gemm_mxfp8|gemm_swiglu|gemm_swiglu_bwd|gemm_rope|flash|flash128|rmsnorm|swiglu|rope|ce|adamw|embedding|quantize}
 pattern=${2:?kernel name pattern, e.g. regex:gemm_tcgen05}
 out=${3:-ncu_out}
 tag=${4:-$target}   # name of the output files (several kernels of one target can be captured one after the other)

@@ -1,7 +1,7 @@
 """Small profiler target: a few launches of one kernel family at a shape larger than L2 but holding only
 a few hundred MB, so an `ncu --set full` capture ends by itself in about a minute.
 
-    python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,gemm_swiglu,gemm_rope,flash,flash128,rmsnorm,swiglu,rope,
+    python benchmarks/kernels/ncu_target.py {gemm,gemm_single,gemm_mxfp8,gemm_swiglu,gemm_swiglu_bwd,gemm_rope,flash,flash128,rmsnorm,swiglu,rope,
                                              ce,adamw,embedding,quantize}[,more targets] [iters]
 """
 
@@ -40,6 +40,12 @@ def build(kind: str):
 
         a, b = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(4096, 768, device=dev, dtype=bf)
         fn = lambda: gemm_swiglu(a, b)  # gate||up projection with the SwiGLU epilogue (gemm2_tcgen05_kernel<1>)
+    elif kind == "gemm_swiglu_bwd":
+        from nanonemo_b200.ops.gemm import gemm_swiglu_bwd
+
+        dy, w_down = torch.randn(M, 768, device=dev, dtype=bf), torch.randn(768, 2048, device=dev, dtype=bf) * 0.03
+        gu = torch.randn(M, 4096, device=dev, dtype=bf)
+        fn = lambda: gemm_swiglu_bwd(dy, w_down, gu)  # down projection's dgrad with the SwiGLU backward epilogue (gemm2_tcgen05_kernel<4>)
     elif kind == "gemm_rope":
         from nanonemo_b200.models.layers import rope_cache
         from nanonemo_b200.ops.gemm import gemm_rope

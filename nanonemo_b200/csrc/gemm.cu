@@ -26,6 +26,8 @@
 
 #include "comm.cuh"
 #include "gemm2.cuh"
+#include <type_traits>
+
 #include "sm100.cuh"
 
 namespace {
@@ -483,24 +485,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld_32x32b_x32(t_row + col0, r0);
           tmem_ld_32x32b_x32(t_row + col0 + 32, r1);
           tmem_ld_wait();
-          const bool is_bf16 = p.out_bf16 != 0;
+          // one branch around the whole conversion (not one per pair): each arm is straight-line code
+          auto convert_row = [&](auto is_bf16) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint32_t w[4];
+            for (int j = 0; j < 8; ++j) {
+              uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = (j & 3) * 8 + 2 * e;
-              const float lo = __uint_as_float(j < 4 ? r0[i] : r1[i]), hi = __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]);
-              if (is_bf16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&v);
+              for (int e = 0; e < 4; ++e) {
+                const int i = (j & 3) * 8 + 2 * e;
+                w[e] = sm100::pack2_16<!decltype(is_bf16)::value>(__uint_as_float(j < 4 ? r0[i] : r1[i]), __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]));
               }
+              *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          };
+          if (p.out_bf16 != 0) convert_row(std::true_type{});
+          else convert_row(std::false_type{});
         }
         fence_proxy_async_smem();
         named_barrier_sync(1, kEpilogueThreads);

@@ -155,7 +155,11 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <int EPI>
+// BF16: the 16-bit format of operands and output (false = fp16). A template parameter rather than a launch argument so that the
+// epilogues' conversions are straight-line code: with a run-time flag every pack / unpack is a branch, the unrolled per-element
+// arithmetic is cut into hundreds of basic blocks and the epilogue warps (two per scheduler at most) lose the overlap between
+// independent elements that hides the special-function and conversion latencies.
+template <int EPI, bool BF16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<EPI>::kThreads, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmE, const Params2 p) {
@@ -356,7 +360,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       const bool rows_live = d_row < p.M;  // an odd number of 128-row blocks leaves the peer's last block outside the matrix
-      const bool bf = p.out_bf16 != 0;
+      constexpr bool bf = BF16;
       const int sw = row & 7;
       if constexpr (EPI == EPI_SWIGLU) {
         // accumulator columns [0, 128) = gate, [128, 256) = up of features n_blk * 128 ...; 64 features per round, all three
@@ -609,11 +613,11 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 namespace {
 
-template <int EPI>
+template <int EPI, bool BF16>
 int max_resident_pairs() {
   static int max_clusters = -1;
   if (max_clusters < 0) {
-    auto kern = gemm2_tcgen05_kernel<EPI>;
+    auto kern = gemm2_tcgen05_kernel<EPI, BF16>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<EPI>::kSmemBytes) != cudaSuccess) {
       nnb_set_error("gemm2: cannot reserve %d bytes of shared memory", Cfg<EPI>::kSmemBytes);
       cudaGetLastError();
@@ -635,10 +639,10 @@ int max_resident_pairs() {
   return max_clusters;
 }
 
-template <int EPI>
+template <int EPI, bool BF16>
 int launch2(const NnbGemm2Args& a, cudaStream_t st) {
   const int sms = a.max_ctas > 0 ? min(a.max_ctas, nnb_num_sms()) : nnb_num_sms();
-  const int resident = max_resident_pairs<EPI>();
+  const int resident = max_resident_pairs<EPI, BF16>();
   if (resident < 0) return resident;
   const int pairs = min(sms / 2, resident);  // persistent pairs must all be resident at once
   if (pairs < 1 || a.M < 2 * BM || a.N < BN / 2) return 1;
@@ -717,7 +721,7 @@ int launch2(const NnbGemm2Args& a, cudaStream_t st) {
   }
   const int items = p.m_pairs * p.n_blocks * p.k_splits;
   const int grid = 2 * min(items, pairs);
-  gemm2_tcgen05_kernel<EPI><<<grid, Cfg<EPI>::kThreads, Cfg<EPI>::kSmemBytes, st>>>(tmA, tmB, tmD, tmE, p);
+  gemm2_tcgen05_kernel<EPI, BF16><<<grid, Cfg<EPI>::kThreads, Cfg<EPI>::kSmemBytes, st>>>(tmA, tmB, tmD, tmE, p);
   NNB_LAUNCH_OK("gemm2_tcgen05");
   return 0;
 }
@@ -726,11 +730,13 @@ int launch2(const NnbGemm2Args& a, cudaStream_t st) {
 
 int nnb_gemm2_launch(const NnbGemm2Args& a, cudaStream_t st) {
   switch (a.epilogue) {
-    case EPI_NONE: return launch2<EPI_NONE>(a, st);
-    case EPI_SWIGLU: return launch2<EPI_SWIGLU>(a, st);
-    case EPI_ROPE: return launch2<EPI_ROPE>(a, st);
-    case EPI_CE_STATS: return launch2<EPI_CE_STATS>(a, st);
-    case EPI_SWIGLU_BWD: return launch2<EPI_SWIGLU_BWD>(a, st);
+#define NNB_LAUNCH2(E) (a.dtype == NNB_BF16 ? launch2<E, true>(a, st) : launch2<E, false>(a, st))
+    case EPI_NONE: return NNB_LAUNCH2(EPI_NONE);
+    case EPI_SWIGLU: return NNB_LAUNCH2(EPI_SWIGLU);
+    case EPI_ROPE: return NNB_LAUNCH2(EPI_ROPE);
+    case EPI_CE_STATS: return NNB_LAUNCH2(EPI_CE_STATS);
+    case EPI_SWIGLU_BWD: return NNB_LAUNCH2(EPI_SWIGLU_BWD);
+#undef NNB_LAUNCH2
     default: nnb_set_error("gemm2: unknown epilogue %d", a.epilogue); return -1;
   }
 }
