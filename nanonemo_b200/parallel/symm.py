@@ -189,12 +189,13 @@ class SymmetricAllReduce:
         if with_norm:
             self.comm.enable_norm_parts()
         # NVSwitch multicast (multimem.ld_reduce / multimem.st): the switch does the sum, so a rank moves the data once instead of
-        # 2 (N - 1) / N times. Opt-in (NANONEMO_MULTIMEM=1): with two ranks the plain path is faster (a single peer load already
-        # is the whole reduction), with four it measured equal in isolation (1.03 vs 1.05 ms for 435 MiB) and inside the
-        # training step (35.6 vs 35.6-35.8 ms). When asked for, it is used only after a small all-reduce through the multicast
+        # 2 (N - 1) / N times. Measured for the 435 MiB gradient: 2 ranks 1.13 vs 0.71 ms (plain peer loads win: a single peer
+        # load already is the whole reduction), 4 ranks 1.03 vs 1.05 ms, 8 ranks 0.99 vs 1.28 ms (NCCL: 1.15 ms). So it is used
+        # from 8 ranks up (NANONEMO_MULTIMEM=1 / 0 forces it on / off), and only after a small all-reduce through the multicast
         # address has given the exact expected values on every rank.
-        want = os.environ.get("NANONEMO_MULTIMEM", "0")
-        self.use_multimem = bool(data.multicast_ptr) and want == "1" and self._multicast_gives_exact_sums(group)
+        want = os.environ.get("NANONEMO_MULTIMEM", "auto")
+        self.use_multimem = (bool(data.multicast_ptr) and (want == "1" or (want == "auto" and data.world >= 8))
+                             and self._multicast_gives_exact_sums(group))
 
     def all_reduce_(self, lo: int, hi: int, scale: float, bucket: int = -1):
         self.comm.all_reduce_(self.data, lo, hi, scale, self.use_multimem, bucket)
