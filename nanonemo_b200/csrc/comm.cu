@@ -48,8 +48,8 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
 }
 
 // WMAX = compile-time bound on the world size, U = independent 16-byte positions per thread: U x WMAX peer loads are issued
-// before the first add. U x WMAX = 8 keeps the kernel within 85 registers (see kCommThreads); one block per SM then has
-// 148 x 256 x 128 B = 4.8 MB in flight, above the NVLink latency-bandwidth product (~3 us x 0.8 TB/s).
+// before the first add. U x WMAX = 8 keeps the kernel within 85 registers (see kCommThreads); two 128-thread blocks per SM
+// then have 296 x 128 x 128 B = 4.8 MB in flight, above the NVLink latency-bandwidth product (~3 us x 0.8 TB/s).
 //
 // Gradient all-reduce (data parallel): in-place two-shot all-reduce of [lo, lo + n) fused with the 1/world average; rank r
 // reduces slice r, writes the result into every peer's buffer and, on the way, sums the squares of its slice. Each block
